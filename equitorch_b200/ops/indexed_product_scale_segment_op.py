@@ -1,0 +1,21 @@
+"""Indexed, scaled products summed over CSR segments.  Presets as in
+``equitorch/ops/indexed_product_scale_segment_op.py:9-147``."""
+from .batched_sparse_dense_op import (indexed_inner_scale_gather, indexed_mul_scale_gather,
+                                      indexed_outer_scale_gather, indexed_vecmat_scale_gather,
+                                      indexed_vecsca_scale_gather)
+
+
+def _preset(fn):
+    def op(input1, input2, scale=None, index1=None, index2=None, seg=None, out=None, **tile_kwargs):
+        assert seg is not None, "seg cannot be None for segment operations"
+        assert index1 is not None or index2 is not None, "At least one of index1 or index2 must be provided"
+        return fn(input1, input2, scale=scale, index1=index1, index2=index2, seg=seg, out=out)
+    op.__name__ = fn.__name__.replace("_scale_gather", "_scale_segment")
+    return op
+
+
+indexed_mul_scale_segment = _preset(indexed_mul_scale_gather)
+indexed_outer_scale_segment = _preset(indexed_outer_scale_gather)
+indexed_inner_scale_segment = _preset(indexed_inner_scale_gather)
+indexed_vecmat_scale_segment = _preset(indexed_vecmat_scale_gather)
+indexed_vecsca_scale_segment = _preset(indexed_vecsca_scale_gather)

@@ -1,0 +1,139 @@
+/*
+ * eqt_b200: C ABI of the sm_100a kernels behind Equitorch's sparse tensor-product path.
+ *
+ * Every entry point takes plain device pointers and sizes, launches on the given CUDA
+ * stream (a cudaStream_t passed as void*; NULL = legacy default stream), never
+ * synchronises, never allocates (except where stated) and returns 0 or an EQT_ERR_* code.
+ * eqt_last_error() returns a static description of the most recent failure of the
+ * calling thread.  Index arrays are int64 on the device, exactly as the reference's
+ * Info tuples hold them; a NULL index array means "identity" (0, 1, 2, ...).
+ *
+ * The "replaces" notes name the reference interface each entry point stands in for
+ * (paths relative to the reference repository root).
+ */
+#ifndef EQT_B200_H
+#define EQT_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum eqt_status {
+  EQT_OK = 0,
+  EQT_ERR_BAD_ARGUMENT = 1,   /* NULL pointer, negative size, unknown enum value            */
+  EQT_ERR_UNSUPPORTED = 2,    /* valid request that no kernel covers (e.g. size limits)     */
+  EQT_ERR_CUDA = 3            /* a CUDA runtime call failed; see eqt_last_error()           */
+};
+
+enum eqt_dtype { EQT_F32 = 0, EQT_F64 = 1, EQT_BF16 = 2 };
+
+/* Which pairwise product is formed for each table entry. */
+enum eqt_op {
+  EQT_OP_MUL = 0,     /* x[.., c]   * y[.., c]                    -> (.., c)       */
+  EQT_OP_VECSCA = 1,  /* x[.., c]   * y[..]   (y has no channel)   -> (.., c)       */
+  EQT_OP_SCALE = 2,   /* x[.., c]             (no second operand)  -> (.., c)       */
+  EQT_OP_OUTER = 3,   /* x[.., c1]  * y[.., c2]                    -> (.., c1, c2)  */
+  EQT_OP_INNER = 4,   /* sum_c x[.., c] * y[.., c]                 -> (..)          */
+  EQT_OP_VECMAT = 5   /* sum_ci x[.., ci] * y[.., ci, co]          -> (.., co)      */
+};
+
+/*
+ * out[n, index_out[o] | o, ...] = sum_{t in [seg[o], seg[o+1])}  scale[t'] * in1[n | -, index1[t'], ..] (op) in2[n | -, index2[t'], ..]
+ * with t' = gather_index[t] (or t).  Without seg there is one entry per computed row (t = o).
+ * With `accumulated` the batch dimension n is summed away and `out` has no batch dimension.
+ *
+ * Layouts are contiguous row-major: in1 (n | 1, rows1, c1), in2 per op (see eqt_op),
+ * out (n, out_size, ...) or (out_size, ...) when accumulated.  `out` must be zero-filled by
+ * the caller when `accumulated` or `index_out` is used; otherwise rows [0, num_out) are
+ * fully overwritten (an empty segment writes zeros).
+ * dtype is the element type of in1, in2 and of a non-accumulated out.  Sums are carried in
+ * float (double for EQT_F64) whatever the storage type; `scale` and an accumulated out have that
+ * arithmetic type (float for EQT_F32 / EQT_BF16, double for EQT_F64).
+ */
+typedef struct eqt_product_args {
+  int32_t op;            /* enum eqt_op                                             */
+  int32_t dtype;         /* enum eqt_dtype                                          */
+  int32_t shared1;       /* in1 has no batch dimension                              */
+  int32_t shared2;       /* in2 has no batch dimension                              */
+  int32_t accumulated;   /* sum over the batch                                      */
+  int32_t reserved;
+  const void* in1;
+  const void* in2;       /* NULL for EQT_OP_SCALE                                   */
+  void* out;
+  const void* scale;     /* (T,) float | double (see above), or NULL (= 1)         */
+  const int64_t* index1; /* (T,) rows of in1, or NULL                               */
+  const int64_t* index2; /* (T,) rows of in2, or NULL                               */
+  const int64_t* seg;    /* (num_out + 1,) CSR pointer into the table, or NULL      */
+  const int64_t* gather_index; /* (seg[num_out],) indirection into the table, or NULL */
+  const int64_t* index_out;    /* (num_out,) output row of each computed row, or NULL */
+  int64_t n;             /* batch size                                              */
+  int64_t rows1;         /* sparse extent of in1                                    */
+  int64_t rows2;         /* sparse extent of in2                                    */
+  int64_t num_out;       /* computed rows                                           */
+  int64_t out_size;      /* rows of the output tensor (>= num_out unless scattered) */
+  int64_t c1;            /* channels of in1 (reduction size for INNER / VECMAT)     */
+  int64_t c2;            /* OUTER: channels of in2; VECMAT: output channels; else 0 */
+} eqt_product_args;
+
+/*
+ * Generic batched sparse-dense product.
+ * replaces: equitorch/ops/batched_sparse_dense_op.py
+ *   indexed_mul_scale_gather :277, indexed_outer_scale_gather :557, indexed_inner_scale_gather :833,
+ *   indexed_vecmat_scale_gather :1511, indexed_vecsca_scale_gather :1796 (and the argument-swapping
+ *   aliases indexed_scavec_scale_gather :994, indexed_mat_t_vec_scale_gather :1200), and
+ *   equitorch/ops/indexed_scale_segment_op.py indexed_scale_segment :172 (EQT_OP_SCALE).
+ */
+int eqt_sparse_product(const eqt_product_args* args, void* stream);
+
+/*
+ * Real spherical harmonics by the degree recurrence
+ *   Y_l[m] = sum_e coef[e] * xyz[axis[e]] * Y_{l-1}[m_in[e]],   Y_0 = 1,
+ * entries of degree l stored in [ptr[l], ptr[l+1]) with m_out ascending.
+ * xyz (n, 3), out (n, (l_max+1)^2), same dtype (EQT_F32 or EQT_F64).  With `normalize` the
+ * vector is divided by max(|v|, 1e-12) first; `out_scale` multiplies every component.
+ * replaces: equitorch/ops/spherical_harmonics.py spherical_harmonics :69 plus the
+ *   normalisation of equitorch/nn/sphericals.py :31-35.
+ */
+typedef struct eqt_sh_table {
+  const int32_t* ptr;    /* (l_max + 2,) device, ptr[0] = ptr[1] = 0                */
+  const int32_t* m_out;  /* (E,) device, component within degree l                  */
+  const int32_t* m_in;   /* (E,) device, component within degree l-1                */
+  const int32_t* axis;   /* (E,) device, 0 = x, 1 = y, 2 = z                        */
+  const double* coef;    /* (E,) device                                             */
+  int32_t l_max;
+  int32_t num_entries;
+} eqt_sh_table;
+
+int eqt_sh_forward(int32_t dtype, const void* xyz, void* out, int64_t n, const eqt_sh_table* table,
+                   int32_t normalize, double out_scale, void* stream);
+
+/* grad_xyz (n, 3) = d(sum out * grad_out)/d xyz, through the normalisation when enabled. */
+int eqt_sh_backward(int32_t dtype, const void* xyz, const void* grad_out, void* grad_xyz, int64_t n,
+                    const eqt_sh_table* table, int32_t normalize, double out_scale, void* stream);
+
+/*
+ * Rows of a node tensor summed over CSR segments of (sorted) edges, and the matching gather.
+ *   eqt_segment_sum: out[d, :] = sum_{e in [ptr[d], ptr[d+1])} in[perm[e] | e, :]
+ *   eqt_gather_rows: out[e, :] = in[index[e], :]
+ * width = elements per row; dtype EQT_F32 / EQT_F64 / EQT_BF16 (sums carried in float).
+ * replaces: the torch_geometric.utils.scatter / segment call and the edge_index gather a user of
+ *   the reference places around the layer (equitorch/transforms/__init__.py :99-101 shows the
+ *   edge_index[0] = source, edge_index[1] = destination convention).
+ */
+int eqt_segment_sum(int32_t dtype, const void* in, const int64_t* ptr, const int64_t* perm, void* out,
+                    int64_t num_segments, int64_t width, void* stream);
+int eqt_gather_rows(int32_t dtype, const void* in, const int64_t* index, void* out, int64_t num_rows,
+                    int64_t width, void* stream);
+
+/* Library / device facts. */
+const char* eqt_last_error(void);
+int eqt_version(void);
+/* Kernel launches issued by this library in the calling process since load (for benchmarks). */
+int64_t eqt_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EQT_B200_H */
