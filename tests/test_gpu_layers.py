@@ -21,7 +21,7 @@ def _check(fn, rec, dtype, what):
 
     def close(got, want, name):
         scale = float(want.abs().max().clamp_min(1e-30))
-        err = float((got.double().cpu() - want).abs().max()) / scale
+        err = float((got.detach().double().cpu() - want).abs().max()) / scale
         assert err < tol, f"{what}: {name} relative error {err:.2e} (tolerance {tol})"
 
     assert out.shape == rec["out"].shape, what
@@ -33,7 +33,13 @@ def _check(fn, rec, dtype, what):
 
 
 def _module(cls, ctor, dtype, **extra):
-    return cls(**ctor, internal_weights=False, **extra).to(DEV, dtype)
+    """Tables are built in the default dtype (as in the reference), so float64 runs build them in float64."""
+    old = torch.get_default_dtype()
+    torch.set_default_dtype(dtype)
+    try:
+        return cls(**ctor, internal_weights=False, **extra).to(DEV)
+    finally:
+        torch.set_default_dtype(old)
 
 
 @pytest.mark.parametrize("dtype", [torch.float64, torch.float32])
@@ -87,11 +93,15 @@ def test_spherical_harmonics_high_degree_and_other_axis():
 
 @pytest.mark.parametrize("dtype", [torch.float64, torch.float32])
 def test_wigner_fixtures(golden_layers, dtype):
-    wig = enn.WignerD(Irreps((0, 3))).to(DEV, dtype)
+    old = torch.get_default_dtype()
+    torch.set_default_dtype(dtype)
+    try:
+        wig, wig2, rot = (enn.WignerD(Irreps((0, 3))).to(DEV), enn.WignerD(Irreps("2x0e+1o+2e")).to(DEV),
+                          enn.SparseWignerRotation(Irreps((0, 2))).to(DEV))
+    finally:
+        torch.set_default_dtype(old)
     _check(lambda a, b, c: wig(a, b, c), golden_layers["wignerd/l3"], dtype, "wignerd/l3")
-    wig2 = enn.WignerD(Irreps("2x0e+1o+2e")).to(DEV, dtype)
     _check(lambda a, b, c: wig2(a, b, c), golden_layers["wignerd/mul"], dtype, "wignerd/mul")
-    rot = enn.SparseWignerRotation(Irreps((0, 2))).to(DEV, dtype)
     _check(lambda x, a, b, c: rot(x, sincos(a, 2), sincos(b, 2), sincos(c, 2)),
            golden_layers["sparse_wigner_rotation/l2"], dtype, "sparse_wigner_rotation/l2")
 
@@ -118,7 +128,7 @@ def test_config1_like_against_oracle(mode, per_sample):
     out_g = layer(xg, enn.SphericalHarmonics(2)(vg), wg)
     gg = torch.autograd.grad(out_g, [xg, vg, wg], cot.to(DEV))
     for name, a, b in [("out", out_g, out_o)] + [(f"grad{n}", a, b) for n, (a, b) in enumerate(zip(gg, go))]:
-        err = float((a.double().cpu() - b.detach()).abs().max() / b.detach().abs().max())
+        err = float((a.detach().double().cpu() - b.detach()).abs().max() / b.detach().abs().max())
         assert err < 1e-5, f"{name}: relative error {err:.2e}"
 
 
@@ -136,7 +146,11 @@ def test_gradcheck_and_gradgradcheck_small():
         (enn.TensorProduct, dict(irreps_in1=ir, irreps_in2=ir, irreps_out=ir, channels_in1=2, channels_in2=3,
                                  channels_out=2, feature_mode="uvw"), [(3, 4, 2), (3, 4, 3)]),
     ]:
-        layer = cls(**ctor, internal_weights=False).to(DEV, torch.float64)
+        torch.set_default_dtype(torch.float64)
+        try:
+            layer = cls(**ctor, internal_weights=False).to(DEV)
+        finally:
+            torch.set_default_dtype(torch.float32)
         ins = [torch.randn(*s, dtype=torch.float64, device=DEV, requires_grad=True) for s in shapes]
         w = torch.randn(*layer.weight_shape, dtype=torch.float64, device=DEV, requires_grad=True)
         assert torch.autograd.gradcheck(lambda a, b, c: layer(a, b, c), (*ins, w), eps=1e-6, atol=1e-5, rtol=1e-5,
