@@ -42,6 +42,12 @@ class ShTable(C.Structure):
                 ("coef", C.c_void_p), ("l_max", C.c_int32), ("num_entries", C.c_int32)]
 
 
+class TpTableStruct(C.Structure):
+    _fields_ = [("scale", C.c_void_p), ("m_feat", C.c_void_p), ("m_y", C.c_void_p), ("row_ptr", C.c_void_p),
+                ("num_entries", C.c_int32), ("num_rows", C.c_int32), ("d_feat", C.c_int32), ("d_y", C.c_int32),
+                ("structure_key", C.c_uint64)]
+
+
 # name -> (restype, argtypes); every symbol declared in include/eqt_b200.h appears here
 SIGNATURES = {
     "eqt_sparse_product": (C.c_int, [C.POINTER(ProductArgs), C.c_void_p]),
@@ -52,6 +58,10 @@ SIGNATURES = {
     "eqt_segment_sum": (C.c_int, [C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
                                   C.c_int64, C.c_void_p]),
     "eqt_gather_rows": (C.c_int, [C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
+    "eqt_tp_cg_segment_sum": (C.c_int, [C.POINTER(TpTableStruct), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                        C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
+    "eqt_tp_cg_inner": (C.c_int, [C.POINTER(TpTableStruct), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                  C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
     "eqt_last_error": (C.c_char_p, []),
     "eqt_version": (C.c_int, []),
     "eqt_launch_count": (C.c_int64, []),

@@ -40,10 +40,10 @@ def sources():
 
 
 def _stale() -> bool:
-    if not os.path.exists(LIB_PATH):
+    if not os.path.exists(LIB_PATH) or not os.path.exists(os.path.join(HERE, "generated", "tp_specs.inc")):
         return True
     built = os.path.getmtime(LIB_PATH)
-    deps = sources() + glob.glob(os.path.join(HERE, "*.cuh")) + glob.glob(os.path.join(HERE, "generated", "*")) \
+    deps = sources() + glob.glob(os.path.join(HERE, "*.cuh")) + glob.glob(os.path.join(HERE, "*.py")) \
         + glob.glob(os.path.join(os.path.dirname(PKG), "include", "*.h"))
     return any(os.path.getmtime(d) > built for d in deps)
 
@@ -52,6 +52,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     """Build if sources are newer than the library; returns the library path."""
     if not force and not _stale():
         return LIB_PATH
+    from .gen_tp_specs import generate
+    generate()
     os.makedirs(LIB_DIR, exist_ok=True)
     obj_dir = os.path.join(LIB_DIR, "obj")
     os.makedirs(obj_dir, exist_ok=True)

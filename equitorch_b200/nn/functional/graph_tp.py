@@ -1,0 +1,104 @@
+"""``SO3Linear`` evaluated on the edges of a graph and summed into destination nodes, fused.
+
+    out[d] = sum_{e: dst(e) = d}  SO3Linear(node_x[src(e)], y[e]; W)
+
+The reference offers the per-edge layer only; users gather ``node_x[edge_index[0]]`` before it and
+scatter-add after it (``equitorch/nn/linears.py:145-187`` surrounded by the
+``edge_index`` convention of ``equitorch/transforms/__init__.py:99-101``).  Here the three steps
+are one operation, and because the weights are shared by all edges the sum over edges is moved
+*in front of* the channel mixing: the CG contraction is accumulated per destination node
+(``S[d, r, :]``, one row per (output component, path)) and the ``C_in x C_out`` matrices are
+applied once per node instead of once per edge - the result is the same sum, evaluated in a
+different order.  The same holds for every gradient:
+
+    grad_W        = sum_d  S[d]^T g[d]                       (node level)
+    G[d]          = g[d] W^T                                 (node level, gradient w.r.t. S)
+    grad_y[e]     = <CG, node_x[src(e)], G[dst(e)]>          (edge pass, grouped by destination)
+    grad_node_x[s]= (sum_{e: src(e)=s} CG' (g[dst(e)], y[e])) W^T   (edge pass grouped by source, then node level)
+
+No per-edge tensor with a channel axis is ever written to memory.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch import Tensor
+from torch.autograd import Function
+
+from ...graph import EdgeGraph
+from ...ops import batched_sparse_dense_op as _ops
+from ...ops.fused_tp_op import TpTable, cg_inner, cg_segment_sum
+from ...structs import TensorProductInfo
+
+
+class GraphTPPlan:
+    """Device tables of one layer for the fused graph kernels (built once per layer and device)."""
+
+    def __init__(self, tp_info_forward: TensorProductInfo, tp_info_backward1: TensorProductInfo,
+                 d_in1: int, d_in2: int, d_out: int, device):
+        f, b1 = tp_info_forward, tp_info_backward1
+        self.fwd_table = TpTable(f.info_Mij_fwd, True, d_in1, d_in2, device)
+        # backward-1 tables: input1 is the channel-less operand, input2 the incoming gradient
+        self.bwd1_table = TpTable(b1.info_Mij_fwd, False, d_out, d_in2, device)
+        self.mix_fwd, self.mix_bwd1, self.mix_bwd2 = (t.to(device) for t in (f.info_M_fwd, f.info_M_bwd1, f.info_M_bwd2))
+        self.mix_src = b1.info_M_fwd.to(device)
+        self.d_in1, self.d_in2, self.d_out = d_in1, d_in2, d_out
+        self.device = torch.device(device)
+
+
+def _mix(s: Tensor, w: Tensor, info, mode: str) -> Tensor:
+    op = _ops.indexed_vecmat_scale_gather if mode == "uv" else _ops.indexed_mul_scale_gather
+    return op(s, w, info.scale, info.index1, info.index2, info.seg_out, out_size=info.out_size)
+
+
+class SO3LinearGraphFunction(Function):
+    @staticmethod
+    def forward(ctx, node_x: Tensor, y: Tensor, weight: Tensor, graph: EdgeGraph, plan: GraphTPPlan, mode: str):
+        s = cg_segment_sum(plan.fwd_table, node_x, y, graph.src_by_dst, graph.dst_order, graph.dst_ptr, graph.num_dst)
+        out = _mix(s, weight, plan.mix_fwd, mode)
+        ctx.save_for_backward(node_x, y, weight, s if weight.requires_grad else None)
+        ctx.graph, ctx.plan, ctx.mode = graph, plan, mode
+        return out
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, grad: Tensor):
+        node_x, y, weight, s = ctx.saved_tensors
+        graph, plan, mode = ctx.graph, ctx.plan, ctx.mode
+        grad = grad.contiguous()
+        gx = gy = gw = None
+        b1, b2 = plan.mix_bwd1, plan.mix_bwd2
+        wt = weight.transpose(-1, -2).contiguous() if mode == "uv" else weight
+        if ctx.needs_input_grad[2]:
+            if mode == "uv":   # (P, Cout, Cin) summed over nodes, then transposed to the weight's layout
+                gw = _ops.indexed_outer_scale_gather(grad, s, b2.scale, b2.index1, b2.index2, b2.seg_out,
+                                                     out_accumulated=True, out_size=b2.out_size)
+                gw = gw.transpose(-1, -2).contiguous()
+            else:
+                gw = _ops.indexed_mul_scale_gather(grad, s, b2.scale, b2.index1, b2.index2, b2.seg_out,
+                                                   out_accumulated=True, out_size=b2.out_size)
+        if ctx.needs_input_grad[1]:
+            # gradient w.r.t. the node-level intermediate: G[d, r] = g[d, M(r)] W[w(r)]^T
+            if mode == "uv":
+                g_inter = _ops.indexed_vecmat_scale_gather(grad, wt, b1.scale, b1.index2, b1.index1, b1.seg_out,
+                                                           out_size=b1.out_size)
+            else:
+                g_inter = _ops.indexed_mul_scale_gather(wt, grad, b1.scale, b1.index1, b1.index2, b1.seg_out,
+                                                        out_size=b1.out_size)
+            gy = cg_inner(plan.fwd_table, node_x, g_inter, graph.src_by_dst, graph.dst_ptr, graph.dst_sorted,
+                          graph.dst_order, y.shape[0])
+        if ctx.needs_input_grad[0]:
+            sx = cg_segment_sum(plan.bwd1_table, grad, y, graph.dst_by_src, graph.src_order, graph.src_ptr,
+                                graph.num_src)
+            gx = _mix(sx, wt, plan.mix_src, mode)
+        return gx, gy, gw, None, None, None
+
+
+def so3_linear_graph(node_x: Tensor, y: Tensor, weight: Tensor, graph: EdgeGraph, plan: GraphTPPlan,
+                     feature_mode: str = "uv") -> Tensor:
+    """Fused gather -> ``SO3Linear`` -> sum over incoming edges.  ``node_x`` (num_src, D1, Cin) float32,
+    ``y`` (E, D2) in the caller's edge order, shared ``weight``; returns (num_dst, Dout, Cout)."""
+    if weight.ndim != (3 if feature_mode == "uv" else 2):
+        raise ValueError("the fused graph layer needs weights shared by all edges")
+    return SO3LinearGraphFunction.apply(node_x, y, weight, graph, plan, feature_mode)

@@ -1,0 +1,43 @@
+"""Graph form of ``SO3Linear``: gather by edge source, tensor product with the edge's spherical
+harmonics, sum into the destination node - one fused operation (see ``functional.graph_tp``)."""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+from torch import Tensor
+
+from ..graph import EdgeGraph
+from .functional.graph_tp import GraphTPPlan, so3_linear_graph
+from .linears import SO3Linear
+
+
+class SO3LinearGraph(SO3Linear):
+    """``out[d] = sum_{e -> d} SO3Linear(node_x[src(e)], y[e])`` with weights shared by all edges.
+
+    Same constructor, parameters and state dict as :class:`SO3Linear`; ``forward`` takes node
+    features ``(num_nodes, irreps_in1.dim, channels_in)``, per-edge harmonics ``(E, irreps_in2.dim)``
+    in the caller's edge order and an :class:`~equitorch_b200.graph.EdgeGraph`.
+    """
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        self._plans: Dict[torch.device, GraphTPPlan] = {}
+
+    def plan(self, device) -> GraphTPPlan:
+        device = torch.device(device)
+        if device not in self._plans:
+            self._plans[device] = GraphTPPlan(self.tp_info_forward, self.tp_info_backward1,
+                                              self.irreps_in1_dim, self.irreps_in2_dim, self.irreps_out_dim, device)
+        return self._plans[device]
+
+    def _apply(self, fn, *args, **kwargs):
+        module = super()._apply(fn, *args, **kwargs)
+        module._plans = {}
+        return module
+
+    def forward(self, node_x: Tensor, edge_sh: Tensor, graph: EdgeGraph, weight: Optional[Tensor] = None) -> Tensor:
+        assert node_x.shape[-2] == self.irreps_in1_dim and edge_sh.shape[-1] == self.irreps_in2_dim
+        assert node_x.shape[0] == graph.num_src and edge_sh.shape[0] == graph.num_edges
+        weight = self._resolve_weight(weight)
+        return so3_linear_graph(node_x, edge_sh, weight, graph, self.plan(node_x.device), self.feature_mode)

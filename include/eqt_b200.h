@@ -127,6 +127,55 @@ int eqt_segment_sum(int32_t dtype, const void* in, const int64_t* ptr, const int
 int eqt_gather_rows(int32_t dtype, const void* in, const int64_t* index, void* out, int64_t num_rows,
                     int64_t width, void* stream);
 
+/*
+ * CG step of a tensor-product layer whose second operand has no channel axis, for one role
+ * assignment: table entry t adds  scale[t] * feat[.., m_feat[t], c] * y[.., m_y[t]]  to intermediate
+ * row r, where the entries of row r are [row_ptr[r], row_ptr[r+1]).  These are the fields of the
+ * reference's SparseProductInfo `info_Mij_fwd` (equitorch/structs/__init__.py:67-81, built by
+ * equitorch/utils/_structs.py:219-227) with the segment pointer kept and the operand roles named.
+ * `structure_key` identifies index structures whose inner loops were unrolled at build time
+ * (0 = unknown: the table-driven kernels are used).
+ */
+typedef struct eqt_tp_table {
+  const float* scale;       /* (T,) device                                            */
+  const int64_t* m_feat;    /* (T,) component of the channelled operand               */
+  const int64_t* m_y;       /* (T,) component of the channel-less operand             */
+  const int64_t* row_ptr;   /* (R + 1,)                                               */
+  int32_t num_entries;      /* T                                                      */
+  int32_t num_rows;         /* R                                                      */
+  int32_t d_feat;           /* components of the channelled operand                   */
+  int32_t d_y;              /* components of the channel-less operand (<= 255)        */
+  uint64_t structure_key;
+} eqt_tp_table;
+
+/*
+ * Gather, CG contraction and sum over the edges of each output node in one pass (float32):
+ *   out[d, r, c] = sum_{e in [seg_ptr[d], seg_ptr[d+1])} sum_{t in row r}
+ *                      scale[t] * y[y_index[e] | e, m_y[t]] * feat[feat_index[e] | e, m_feat[t], c]
+ * feat (rows, d_feat, channels), y (.., d_y), out (num_out, R, channels).  seg_ptr == NULL means one
+ * edge per output row (num_out == num_edges, no reduction): the plain per-sample CG step.
+ * `status` points to a device int that is set to 1 if a bounded wait inside the kernel gave up.
+ * replaces: the chain  x[edge_index[0]] -> indexed_vecsca_scale_gather (equitorch/ops/
+ *   batched_sparse_dense_op.py:1796, called from equitorch/nn/functional/linears.py:262) ->
+ *   torch_geometric scatter-sum over edge_index[1]; with the roles of the backward-1 tables it is
+ *   the scavec step of tensor_product_1vu (linears.py:341-363) summed over edge sources.
+ */
+int eqt_tp_cg_segment_sum(const eqt_tp_table* table, const float* feat, const int64_t* feat_index,
+                          const float* y, const int64_t* y_index, const int64_t* seg_ptr, float* out,
+                          int64_t num_out, int64_t num_edges, int32_t channels, int32_t* status, void* stream);
+
+/*
+ * Adjoint of the CG step with respect to the channel-less operand (float32):
+ *   grad_y[y_index[e] | e, k] = sum_{t: m_y[t] = k} scale[t] * sum_c feat[feat_index[e] | e, m_feat[t], c] * g[node(e), row(t), c]
+ * g (num_nodes, R, channels) holds the gradient with respect to the intermediate, already summed
+ * per node; edges are sorted by node (seg_ptr, and edge_node for the table-driven kernel).
+ * replaces: indexed_inner_scale_gather on the `info_Mij_bwd2` table (equitorch/nn/functional/
+ *   linears.py:308-311) fed with per-edge copies of g.
+ */
+int eqt_tp_cg_inner(const eqt_tp_table* table, const float* feat, const int64_t* feat_index, const float* g,
+                    const int64_t* seg_ptr, const int64_t* edge_node, const int64_t* y_index, float* grad_y,
+                    int64_t num_nodes, int64_t num_edges, int32_t channels, int32_t* status, void* stream);
+
 /* Library / device facts. */
 const char* eqt_last_error(void);
 int eqt_version(void);
