@@ -1,0 +1,353 @@
+"""Benchmark of the hot path: edges/s of the Clebsch-Gordan tensor-product layer, forward + backward
+(l_max = 3, 64 channels, full 64 -> 64 channel mixing per path), on N GPUs of one box.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg5|cfg2] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One step = one pass of the layer over one synthetic graph: spherical harmonics of the edge vectors,
+gather of node features by edge source, CG tensor product with shared uvw weights, sum into
+destination nodes, and the backward pass for node features, edge vectors and weights.
+
+Workloads (seeded synthetic data, shapes of the benchmark configurations):
+  cfg5  random geometric graph, 100k nodes, ~2M edges (degree 20), Morton-ordered node ids.  Used at
+        every N (strong scaling): edges are sharded by destination-node range, halo node rows travel
+        by NCCL all-to-all.  The working set (410 MB of node features, 2.5 GB of per-node
+        intermediates) is far larger than the 126 MB L2, so no explicit flush is needed.
+  cfg2  200k edges with uniformly random sources over 10k nodes (single GPU).  Its node table fits in
+        L2, so L2 is flushed between steps and every step is timed on its own.
+
+Rank 0 prints ONE JSON line.  ``value`` is device-timed with inputs resident in HBM; ``e2e`` moves the
+step's inputs from pinned host memory and the result back inside the timed region; ``roofline``
+describes the kernel that takes the largest share of the step; ``cpu_baseline`` times the CPU oracle
+(a port of the reference's algorithm) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+IRREPS = "0e+1o+2e+3o"
+L_MAX, CHANNELS, DIM, ROWS, PATHS = 3, 64, 16, 99, 23
+METRIC = "edges/s, CG tensor product fwd+bwd (lmax=3, C=64)"
+
+
+# ----------------------------------------------------------------------------------------------
+def make_workload(name: str):
+    from equitorch_b200.utils.synthetic import node_features, radius_graph, random_graph
+    if name == "cfg5":
+        graph, _ = radius_graph(100_000, 2_000_000, seed=0)
+        label = "cfg5: random geometric graph, 100k nodes, ~2M edges (avg degree 20), Morton-ordered ids"
+    elif name == "cfg2":
+        graph = random_graph(10_000, 200_000, seed=0)
+        label = "cfg2: 200k edges, uniform random src over 10k nodes, dst sorted"
+    else:
+        raise SystemExit(f"unknown workload {name}")
+    x = node_features(graph.num_nodes, DIM, CHANNELS, seed=1)
+    gen = torch.Generator().manual_seed(2)
+    cot = torch.randn(graph.num_nodes, DIM, CHANNELS, generator=gen)
+    weight = (torch.rand(PATHS, CHANNELS, CHANNELS, generator=gen) * 2 - 1) * (3.0 / CHANNELS) ** 0.5
+    return graph, x, cot, weight, label
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return dict(hbm_gbs=float(d["hbm_gbs"]), source="measured")
+    return dict(hbm_gbs=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows, self.proc, self.thread, self.gpu = [], None, None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return self
+        self.thread = threading.Thread(target=lambda: self.rows.extend(self.proc.stdout), daemon=True)
+        self.thread.start()
+        return self
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.thread.join(timeout=2)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for row in self.rows:
+            parts = [p.strip() for p in row.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            reasons.update(n for n, v in zip(names, parts[2:6]) if v.lower().startswith("active"))
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU arm: the oracle (a CPU port of the reference's algorithm) on a bounded sample of the workload
+# ----------------------------------------------------------------------------------------------
+def cpu_sample_step(graph, x, cot, weight, max_edges: int):
+    """Forward + backward of the oracle on the first destination nodes holding ~max_edges edges."""
+    from oracle import tensor_products as otp
+    n_edges = min(max_edges, graph.src.numel())
+    last_node = int(graph.dst[n_edges - 1])
+    n_edges = int(torch.searchsorted(graph.dst, torch.tensor(last_node), right=True))
+    src, dst, vec = graph.src[:n_edges], graph.dst[:n_edges], graph.edge_vec[:n_edges]
+    xs = x.clone().requires_grad_(True)
+    vs = vec.clone().requires_grad_(True)
+    ws = weight.clone().requires_grad_(True)
+    t0 = time.perf_counter()
+    out = otp.so3_linear_message_passing(xs, vs, src, dst, ws, IRREPS, IRREPS, IRREPS, feature_mode="uv",
+                                         num_out_nodes=last_node + 1)
+    torch.autograd.grad(out, [xs, vs, ws], cot[: last_node + 1])
+    return n_edges, time.perf_counter() - t0
+
+
+def cpu_baseline(graph, x, cot, weight, max_edges=32768, repeats=2):
+    torch.set_num_threads(os.cpu_count() or 1)
+    best, n_edges = None, 0
+    for _ in range(repeats + 1):              # first run warms up the allocator and thread pool
+        n_edges, dt = cpu_sample_step(graph, x, cot, weight, max_edges)
+        best = dt if best is None else min(best, dt)
+    return {"value": n_edges / best, "unit": "edges/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"first {n_edges} edges (by destination) of the workload, fwd+bwd, float32, best of {repeats}"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    graph, x, cot, weight, label = make_workload(args.workload)
+    torch.set_num_threads(os.cpu_count() or 1)
+    max_edges = 32768
+    for _ in range(args.warmup):
+        cpu_sample_step(graph, x, cot, weight, max_edges)
+    total_edges, total_time = 0, 0.0
+    for _ in range(args.steps):
+        n, dt = cpu_sample_step(graph, x, cot, weight, max_edges)
+        total_edges += n
+        total_time += dt
+    value = total_edges / total_time
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "edges/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total_time / max(1, args.steps),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": label, "note": "CPU port of the reference's algorithm (oracle/), all host threads; "
+                   f"each step is a bounded sample of {total_edges // max(1, args.steps)} edges of the workload"},
+        "cpu_baseline": {"value": value, "unit": "edges/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": f"{total_edges // max(1, args.steps)} edges per step"},
+        "e2e": {"value": value, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+# ----------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="cfg5", choices=["cfg5", "cfg2"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch.distributed as dist
+    from equitorch_b200 import _lib, _profile
+    from equitorch_b200 import nn as enn
+    from equitorch_b200.dist import halo_exchange, plan_shards, replicated
+    from equitorch_b200.graph import EdgeGraph
+    from equitorch_b200.ops.fused_tp_op import check_status
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    if args.workload == "cfg2" and world > 1:
+        raise SystemExit("cfg2 is the single-GPU microbenchmark")
+
+    graph, x_all, cot_all, weight, label = make_workload(args.workload)
+    plan = plan_shards(graph.src, graph.dst, graph.num_nodes, world)[rank]
+    lo, hi, e0, e1 = plan.node_lo, plan.node_hi, plan.edge_lo, plan.edge_hi
+    n_edges_total, n_edges_local = graph.src.numel(), e1 - e0
+
+    x_host = x_all[lo:hi].contiguous().pin_memory()
+    vec_host = graph.edge_vec[e0:e1].contiguous().pin_memory()
+    cot = cot_all[lo:hi].contiguous().to(dev)
+    egraph = EdgeGraph(plan.src_local.to(dev), plan.dst_local.to(dev), plan.num_local, plan.num_owned)
+    send_index = plan.send_index.to(dev)
+    layer = enn.SO3LinearGraph(IRREPS, IRREPS, IRREPS, CHANNELS, CHANNELS, feature_mode="uv").to(dev)
+    with torch.no_grad():
+        layer.weight.copy_(weight)
+    sh = enn.SphericalHarmonics(L_MAX)
+    x_dev = x_host.to(dev).requires_grad_(True)
+    vec_dev = vec_host.to(dev).requires_grad_(True)
+    loss_host = torch.empty(1, dtype=torch.float32).pin_memory()
+    gw_host = torch.empty(PATHS, CHANNELS, CHANNELS).pin_memory()
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev) if args.workload == "cfg2" else None
+
+    def step(x, vec):
+        local = halo_exchange(x, plan, send_index) if world > 1 else x
+        w = replicated(layer.weight) if world > 1 else layer.weight
+        out = layer(local, sh(vec), egraph, w)
+        gx, gv, gw = torch.autograd.grad(out, [x, vec, layer.weight], cot)
+        return out, gx, gv, gw
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(max(args.warmup, 3)):      # at least three untimed steps
+        step(x_dev, vec_dev)
+    check_status()
+
+    # ---- device-resident timing -----------------------------------------------------------
+    sampler = ClockSampler(local_rank).start()
+    _profile.enable(True)
+    launches0 = _lib.launch_count()
+    barrier()
+    if flush is None:
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(args.steps):
+            step(x_dev, vec_dev)
+        t1.record()
+        barrier()
+        elapsed_ms = t0.elapsed_time(t1)
+    else:
+        pairs = []
+        for _ in range(args.steps):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            step(x_dev, vec_dev)
+            b.record()
+            pairs.append((a, b))
+        barrier()
+        elapsed_ms = sum(a.elapsed_time(b) for a, b in pairs)
+    launches = _lib.launch_count() - launches0
+    kernels = _profile.collect()
+    _profile.enable(False)
+    clocks = sampler.stop()
+    check_status()
+
+    # ---- end-to-end timing: host buffers in, result out, every step ----------------------------
+    barrier()
+    e0_, e1_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0_.record()
+    for _ in range(args.steps):
+        xd = x_host.to(dev, non_blocking=True).requires_grad_(True)
+        vd = vec_host.to(dev, non_blocking=True).requires_grad_(True)
+        out, gx, gv, gw = step(xd, vd)
+        loss_host.copy_((out * cot).sum().reshape(1), non_blocking=True)
+        gw_host.copy_(gw, non_blocking=True)
+        torch.cuda.current_stream(dev).synchronize()
+    e1_.record()
+    barrier()
+    e2e_ms = e0_.elapsed_time(e1_)
+    check_status()
+
+    times = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    elapsed_ms, e2e_ms = (float(v) for v in times.tolist())
+    steps = max(1, args.steps)
+    value = n_edges_total * steps / (elapsed_ms * 1e-3)
+    e2e_value = n_edges_total * steps / (e2e_ms * 1e-3)
+
+    # ---- roofline of the kernel with the largest share -------------------------------------------
+    n_dst, n_src = plan.num_owned, plan.num_local
+    s_bytes = ROWS * CHANNELS * 4
+    row_bytes = DIM * CHANNELS * 4
+    algorithmic = {   # bytes one launch must move (this rank's shard)
+        "cg_segment_sum[fwd]": n_edges_local * (row_bytes + DIM * 4 + 8) + n_dst * (s_bytes + 8),
+        "cg_segment_sum[grad_x]": n_edges_local * (row_bytes + DIM * 4 + 16) + n_src * (s_bytes + 8),
+        "cg_inner[grad_y]": n_edges_local * (row_bytes + DIM * 4 + 8) + n_dst * (s_bytes + 8),
+        "channel_mix[fwd]": n_dst * (s_bytes + row_bytes) + PATHS * CHANNELS * CHANNELS * 4,
+        "channel_mix[grad_inter]": n_dst * (s_bytes + row_bytes) + PATHS * CHANNELS * CHANNELS * 4,
+        "channel_mix[grad_x]": n_src * (s_bytes + row_bytes) + PATHS * CHANNELS * CHANNELS * 4,
+        "weight_grad": n_dst * (s_bytes + row_bytes) + PATHS * CHANNELS * CHANNELS * 4,
+        "spherical_harmonics[fwd]": n_edges_local * (12 + DIM * 4),
+        "spherical_harmonics[bwd]": n_edges_local * (12 + DIM * 4 + 12),
+    }
+    pk = peaks()
+    table = {}
+    tracked_ms = sum(ms for _, ms in kernels.values())
+    for name, (count, ms) in sorted(kernels.items(), key=lambda kv: -kv[1][1]):
+        per_launch_ms = ms / max(1, count)
+        gbs = algorithmic.get(name, 0) / (per_launch_ms * 1e-3) / 1e9 if per_launch_ms > 0 else 0.0
+        table[name] = {"launches": count, "ms_per_launch": round(per_launch_ms, 4),
+                       "share": round(ms / tracked_ms, 4) if tracked_ms else None,
+                       "algorithmic_GBps": round(gbs, 1), "frac_of_hbm_peak": round(gbs / pk["hbm_gbs"], 4)}
+    top = next(iter(table)) if table else None
+    roofline = None
+    if top:
+        roofline = {"kernel": top, "bound": "hbm", "achieved": table[top]["algorithmic_GBps"], "peak": pk["hbm_gbs"],
+                    "unit": "GB/s", "frac": table[top]["frac_of_hbm_peak"], "peak_source": pk["source"],
+                    "algorithmic_bytes_per_launch": algorithmic.get(top), "traffic": None}
+
+    result = {
+        "metric": METRIC, "value": value, "unit": "edges/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": elapsed_ms / steps, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": label, "edges": n_edges_total, "nodes": graph.num_nodes, "irreps": IRREPS,
+                   "channels": CHANNELS, "feature_mode": "uv", "paths": PATHS,
+                   "parallelism": f"edges sharded by destination-node range over {world} GPU(s), halo rows by all-to-all",
+                   "l2": ("working set >> 126 MB L2, no flush" if flush is None
+                          else "256 MB written between steps to flush L2; steps timed individually")},
+        "e2e": {"value": e2e_value, "unit": "edges/s", "ms_per_step": e2e_ms / steps,
+                "h2d_bytes_per_step": int(x_host.numel() * 4 + vec_host.numel() * 4) * world if world == 1
+                else int(x_all.numel() * 4 + graph.edge_vec.numel() * 4),
+                "d2h_bytes_per_step": int(4 + gw_host.numel() * 4) * world},
+        "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "kernels": table,
+    }
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            result["cpu_baseline"] = cpu_baseline(graph, x_all, cot_all, weight)
+        print(json.dumps(result))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -26,6 +26,7 @@ import torch
 from torch import Tensor
 from torch.autograd import Function
 
+from ... import _profile
 from ...graph import EdgeGraph
 from ...ops import batched_sparse_dense_op as _ops
 from ...ops.fused_tp_op import TpTable, cg_inner, cg_segment_sum
@@ -55,8 +56,11 @@ def _mix(s: Tensor, w: Tensor, info, mode: str) -> Tensor:
 class SO3LinearGraphFunction(Function):
     @staticmethod
     def forward(ctx, node_x: Tensor, y: Tensor, weight: Tensor, graph: EdgeGraph, plan: GraphTPPlan, mode: str):
-        s = cg_segment_sum(plan.fwd_table, node_x, y, graph.src_by_dst, graph.dst_order, graph.dst_ptr, graph.num_dst)
-        out = _mix(s, weight, plan.mix_fwd, mode)
+        with _profile.timed("cg_segment_sum[fwd]"):
+            s = cg_segment_sum(plan.fwd_table, node_x, y, graph.src_by_dst, graph.dst_order, graph.dst_ptr,
+                               graph.num_dst)
+        with _profile.timed("channel_mix[fwd]"):
+            out = _mix(s, weight, plan.mix_fwd, mode)
         ctx.save_for_backward(node_x, y, weight, s if weight.requires_grad else None)
         ctx.graph, ctx.plan, ctx.mode = graph, plan, mode
         return out
@@ -71,27 +75,32 @@ class SO3LinearGraphFunction(Function):
         b1, b2 = plan.mix_bwd1, plan.mix_bwd2
         wt = weight.transpose(-1, -2).contiguous() if mode == "uv" else weight
         if ctx.needs_input_grad[2]:
-            if mode == "uv":   # (P, Cout, Cin) summed over nodes, then transposed to the weight's layout
-                gw = _ops.indexed_outer_scale_gather(grad, s, b2.scale, b2.index1, b2.index2, b2.seg_out,
-                                                     out_accumulated=True, out_size=b2.out_size)
-                gw = gw.transpose(-1, -2).contiguous()
-            else:
-                gw = _ops.indexed_mul_scale_gather(grad, s, b2.scale, b2.index1, b2.index2, b2.seg_out,
-                                                   out_accumulated=True, out_size=b2.out_size)
+            with _profile.timed("weight_grad"):
+                if mode == "uv":   # (P, Cout, Cin) summed over nodes, then transposed to the weight's layout
+                    gw = _ops.indexed_outer_scale_gather(grad, s, b2.scale, b2.index1, b2.index2, b2.seg_out,
+                                                         out_accumulated=True, out_size=b2.out_size)
+                    gw = gw.transpose(-1, -2).contiguous()
+                else:
+                    gw = _ops.indexed_mul_scale_gather(grad, s, b2.scale, b2.index1, b2.index2, b2.seg_out,
+                                                       out_accumulated=True, out_size=b2.out_size)
         if ctx.needs_input_grad[1]:
             # gradient w.r.t. the node-level intermediate: G[d, r] = g[d, M(r)] W[w(r)]^T
-            if mode == "uv":
-                g_inter = _ops.indexed_vecmat_scale_gather(grad, wt, b1.scale, b1.index2, b1.index1, b1.seg_out,
-                                                           out_size=b1.out_size)
-            else:
-                g_inter = _ops.indexed_mul_scale_gather(wt, grad, b1.scale, b1.index1, b1.index2, b1.seg_out,
-                                                        out_size=b1.out_size)
-            gy = cg_inner(plan.fwd_table, node_x, g_inter, graph.src_by_dst, graph.dst_ptr, graph.dst_sorted,
-                          graph.dst_order, y.shape[0])
+            with _profile.timed("channel_mix[grad_inter]"):
+                if mode == "uv":
+                    g_inter = _ops.indexed_vecmat_scale_gather(grad, wt, b1.scale, b1.index2, b1.index1, b1.seg_out,
+                                                               out_size=b1.out_size)
+                else:
+                    g_inter = _ops.indexed_mul_scale_gather(wt, grad, b1.scale, b1.index1, b1.index2, b1.seg_out,
+                                                            out_size=b1.out_size)
+            with _profile.timed("cg_inner[grad_y]"):
+                gy = cg_inner(plan.fwd_table, node_x, g_inter, graph.src_by_dst, graph.dst_ptr, graph.dst_sorted,
+                              graph.dst_order, y.shape[0])
         if ctx.needs_input_grad[0]:
-            sx = cg_segment_sum(plan.bwd1_table, grad, y, graph.dst_by_src, graph.src_order, graph.src_ptr,
-                                graph.num_src)
-            gx = _mix(sx, wt, plan.mix_src, mode)
+            with _profile.timed("cg_segment_sum[grad_x]"):
+                sx = cg_segment_sum(plan.bwd1_table, grad, y, graph.dst_by_src, graph.src_order, graph.src_ptr,
+                                    graph.num_src)
+            with _profile.timed("channel_mix[grad_x]"):
+                gx = _mix(sx, wt, plan.mix_src, mode)
         return gx, gy, gw, None, None, None
 
 

@@ -11,7 +11,7 @@ from typing import Dict, Tuple
 import torch
 from torch import Tensor
 
-from .. import _lib
+from .. import _lib, _profile
 from ..sh_tables import sh_recurrence
 
 _TABLES: Dict[Tuple[int, torch.device], Tuple[_lib.ShTable, tuple]] = {}
@@ -57,13 +57,15 @@ class _SphericalHarmonics(torch.autograd.Function):
     def forward(ctx, xyz, l_max, normalize, out_scale):
         ctx.save_for_backward(xyz)
         ctx.cfg = (l_max, normalize, out_scale)
-        return sh_forward(xyz, l_max, normalize, out_scale)
+        with _profile.timed("spherical_harmonics[fwd]"):
+            return sh_forward(xyz, l_max, normalize, out_scale)
 
     @staticmethod
     @torch.autograd.function.once_differentiable
     def backward(ctx, grad_out):
         (xyz,) = ctx.saved_tensors
-        return sh_backward(xyz, grad_out, *ctx.cfg), None, None, None
+        with _profile.timed("spherical_harmonics[bwd]"):
+            return sh_backward(xyz, grad_out, *ctx.cfg), None, None, None
 
 
 def spherical_harmonics_fused(input: Tensor, l_max: int, normalize: bool = False, out_scale: float = 1.0) -> Tensor:
