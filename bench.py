@@ -13,6 +13,7 @@ Workloads (seeded synthetic data, shapes of the benchmark configurations):
         every N (strong scaling): edges are sharded by destination-node range, halo node rows travel
         by NCCL all-to-all.  The working set (410 MB of node features, 2.5 GB of per-node
         intermediates) is far larger than the 126 MB L2, so no explicit flush is needed.
+  cfg5q a quarter-size cfg5 (25k nodes, ~500k edges) for profiler captures.
   cfg2  200k edges with uniformly random sources over 10k nodes (single GPU).  Its node table fits in
         L2, so L2 is flushed between steps and every step is timed on its own.
 
@@ -49,6 +50,9 @@ def make_workload(name: str):
     if name == "cfg5":
         graph, _ = radius_graph(100_000, 2_000_000, seed=0)
         label = "cfg5: random geometric graph, 100k nodes, ~2M edges (avg degree 20), Morton-ordered ids"
+    elif name == "cfg5q":   # quarter-size cfg5 for profiler captures (node table 102 MB: still larger than L2)
+        graph, _ = radius_graph(25_000, 500_000, seed=0)
+        label = "cfg5q: random geometric graph, 25k nodes, ~500k edges (avg degree 20), Morton-ordered ids"
     elif name == "cfg2":
         graph = random_graph(10_000, 200_000, seed=0)
         label = "cfg2: 200k edges, uniform random src over 10k nodes, dst sorted"
@@ -177,7 +181,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="cfg5", choices=["cfg5", "cfg2"])
+    ap.add_argument("--workload", default="cfg5", choices=["cfg5", "cfg2", "cfg5q"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -214,9 +218,9 @@ def main():
     cot = cot_all[lo:hi].contiguous().to(dev)
     egraph = EdgeGraph(plan.src_local.to(dev), plan.dst_local.to(dev), plan.num_local, plan.num_owned)
     send_index = plan.send_index.to(dev)
-    layer = enn.SO3LinearGraph(IRREPS, IRREPS, IRREPS, CHANNELS, CHANNELS, feature_mode="uv").to(dev)
-    with torch.no_grad():
-        layer.weight.copy_(weight)
+    layer = enn.SO3LinearGraph(IRREPS, IRREPS, IRREPS, CHANNELS, CHANNELS, internal_weights=False,
+                               feature_mode="uv").to(dev)
+    w_dev = weight.to(dev).requires_grad_(True)
     sh = enn.SphericalHarmonics(L_MAX)
     x_dev = x_host.to(dev).requires_grad_(True)
     vec_dev = vec_host.to(dev).requires_grad_(True)
@@ -226,9 +230,9 @@ def main():
 
     def step(x, vec):
         local = halo_exchange(x, plan, send_index) if world > 1 else x
-        w = replicated(layer.weight) if world > 1 else layer.weight
+        w = replicated(w_dev) if world > 1 else w_dev
         out = layer(local, sh(vec), egraph, w)
-        gx, gv, gw = torch.autograd.grad(out, [x, vec, layer.weight], cot)
+        gx, gv, gw = torch.autograd.grad(out, [x, vec, w_dev], cot)
         return out, gx, gv, gw
 
     def barrier():
