@@ -48,6 +48,11 @@ class TpTableStruct(C.Structure):
                 ("structure_key", C.c_uint64)]
 
 
+class MixBlockStruct(C.Structure):
+    _fields_ = [("in_row0", C.c_int32), ("out_row0", C.c_int32), ("dim", C.c_int32), ("paths", C.c_int32),
+                ("w_offset", C.c_int64)]
+
+
 # name -> (restype, argtypes); every symbol declared in include/eqt_b200.h appears here
 SIGNATURES = {
     "eqt_sparse_product": (C.c_int, [C.POINTER(ProductArgs), C.c_void_p]),
@@ -62,6 +67,8 @@ SIGNATURES = {
                                         C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
     "eqt_tp_cg_inner": (C.c_int, [C.POINTER(TpTableStruct), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                   C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]),
+    "eqt_mix_tc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32,
+                             C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
     "eqt_last_error": (C.c_char_p, []),
     "eqt_version": (C.c_int, []),
     "eqt_launch_count": (C.c_int64, []),

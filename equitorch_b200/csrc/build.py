@@ -43,7 +43,7 @@ def _stale() -> bool:
     if not os.path.exists(LIB_PATH) or not os.path.exists(os.path.join(HERE, "generated", "tp_specs.inc")):
         return True
     built = os.path.getmtime(LIB_PATH)
-    deps = sources() + glob.glob(os.path.join(HERE, "*.cuh")) + glob.glob(os.path.join(HERE, "*.py")) \
+    deps = sources() + glob.glob(os.path.join(HERE, "*.cuh")) + glob.glob(os.path.join(HERE, "*.inc")) + glob.glob(os.path.join(HERE, "*.py")) \
         + glob.glob(os.path.join(os.path.dirname(PKG), "include", "*.h"))
     return any(os.path.getmtime(d) > built for d in deps)
 

@@ -1,0 +1,255 @@
+// Node-level channel mixing on the 5th-generation tensor cores (tcgen05, accumulators in TMEM).
+//
+// For one output irrep (a "block": `dim` components, `paths` coupling paths into it) the weight
+// step of the layer is a plain GEMM
+//
+//     out[(node, m), co] = sum_{kk} A[(node, m), kk] * Bt[co, kk],      kk = (path, ci)
+//
+// because the intermediate rows of a fixed output component are contiguous in memory: row
+// (node, m) of A is the slice S[node, in_row0 + m*paths : in_row0 + (m+1)*paths, :] of the
+// per-node intermediate, K = paths * C_in floats long.  A is described to TMA as a 3-D tensor
+// (kk, m, node) so that one box of (32 floats, dim, nodes_per_tile) lands in shared memory as up
+// to 128 consecutive 128-byte rows in the 128B-swizzled K-major layout tcgen05.mma reads.
+//
+// Precision: float32 results are required to 1e-5, which a single TF32 product (10 mantissa
+// bits) cannot give.  Each operand is split as x = big + small with big = x with the 13 low
+// mantissa bits cleared (exactly representable in TF32) and small = x - big (exact), and three
+// kind::tf32 MMAs accumulate big*big + big*small + small*big in float32 in TMEM; the dropped
+// small*small term is below 2^-22 relative.  The weights are split once on the host side of the
+// call, the activations by four "splitter" warps between the TMA arrival and the MMA issue.
+//
+// Roles inside a CTA of 10 warps (one persistent CTA per SM, tiles of up to 128 (node, m) rows):
+//   warp 0      TMA producer (one elected lane), ring of `stages` k-blocks of 32 floats
+//   warp 1      TMEM allocation, MMA issue (one elected lane), tcgen05.commit to free stages
+//   warps 2-5   split A in place (big) and into a second buffer (small), fence to the async proxy
+//   warps 6-9   epilogue: tcgen05.ld of the finished accumulator (double buffered in TMEM),
+//               float4 stores of the valid rows
+// Every wait on an mbarrier is bounded; on expiry the kernel raises the status flag, stops
+// issuing work, frees its TMEM and returns.
+#include <cuda.h>
+
+#include <algorithm>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace eqt {
+namespace {
+
+constexpr int TC_THREADS = 320;
+constexpr int KB = 32;                 // floats per k-block = one 128-byte swizzle row
+constexpr int TILE_M = 128;
+constexpr int TC_WAIT_SPINS = 1 << 21;
+
+struct MixArgs {
+  float* out;          // (n, D, cout)
+  int64_t n;           // nodes
+  int dim;             // components of the output irrep
+  int npt;             // nodes per tile (npt * dim <= 128)
+  int kblocks;         // K / 32
+  int cout;            // N
+  int D;               // components per node in `out`
+  int out_row0;        // first component of this block in `out`
+  int stages;
+  int tmem_cols;       // power of two >= 2 * cout
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t s32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void bar_init(uint64_t* b, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s32(b)), "r"(count));
+}
+__device__ __forceinline__ void bar_arrive(uint64_t* b) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s32(b)) : "memory");
+}
+__device__ __forceinline__ void bar_expect_tx(uint64_t* b, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool bar_try(uint64_t* b, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(s32(b)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait that also gives up as soon as another role has raised the abort flag.
+__device__ __forceinline__ bool bar_wait(uint64_t* b, uint32_t parity, volatile int* abort_flag) {
+  for (int i = 0; i < TC_WAIT_SPINS; ++i) {
+    if (bar_try(b, parity)) return true;
+    if ((i & 63) == 63) {
+      if (*abort_flag) return false;
+      __nanosleep(128);
+    }
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(s32(dst)), "l"(map), "r"(s32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(s32(dst)), "l"(map), "r"(s32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+
+// K-major, 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart; descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_byte_addr) {
+  return (uint64_t)((smem_byte_addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// kind::tf32, D = f32, A and B K-major, M = 128, N = n
+__host__ __device__ inline uint32_t umma_idesc_tf32(int n) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
+}
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(s32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// round to nearest TF32 (10 mantissa bits); the result is a float whose 13 low mantissa bits are zero
+__device__ __forceinline__ float rn_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+}  // namespace
+}  // namespace eqt
+
+#include "mix_tc_kernel.inc"
+
+// ------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------
+namespace eqt {
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+int make_map(CUtensorMap* map, const float* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides_bytes,
+             const cuuint32_t* box) {
+  EncodeTiledFn enc = encode_tiled();
+  if (!enc) return fail(EQT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint32_t ones[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<float*>(base), dims,
+                   strides_bytes, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(EQT_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return EQT_OK;
+}
+
+int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+}  // namespace
+}  // namespace eqt
+
+extern "C" int eqt_mix_tc(const float* s, const float* w_big, const float* w_small, float* out, int64_t n,
+                          int32_t rows, int32_t comps, int32_t cin, int32_t cout, const eqt_mix_block* blocks,
+                          int32_t num_blocks, int32_t* status, void* stream) {
+  using namespace eqt;
+  if (n < 0 || rows <= 0 || comps <= 0 || cin <= 0 || cout <= 0 || num_blocks < 0) return fail(EQT_ERR_BAD_ARGUMENT, "bad sizes");
+  if (n == 0 || num_blocks == 0) return EQT_OK;
+  if (!s || !w_big || !w_small || !out || !blocks || !status) return fail(EQT_ERR_BAD_ARGUMENT, "NULL pointer");
+  if (cin % KB != 0 || cout % 16 != 0 || cout > 256) return fail(EQT_ERR_UNSUPPORTED, "tensor-core mix needs C_in %% 32 == 0 and C_out %% 16 == 0, C_out <= 256");
+  if ((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(w_big) | reinterpret_cast<uintptr_t>(w_small) |
+       reinterpret_cast<uintptr_t>(out)) & 15u)
+    return fail(EQT_ERR_UNSUPPORTED, "tensor-core mix needs 16-byte aligned operands");
+  if (n * 1ll > 0x7fffffffll) return fail(EQT_ERR_UNSUPPORTED, "too many nodes for one TMA coordinate");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  const uint32_t a_bytes = TILE_M * KB * 4, b_bytes = (uint32_t)cout * KB * 4;
+  const uint32_t stage_bytes = 2 * a_bytes + 2 * b_bytes;
+  int stages = (int)std::min<size_t>(8, (220 * 1024 - 1024) / stage_bytes);
+  if (stages < 2) return fail(EQT_ERR_UNSUPPORTED, "C_out too large for the shared-memory ring");
+  const size_t smem = (size_t)stages * stage_bytes + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(mix_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    if (e != cudaSuccess) return fail(EQT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  int tmem_cols = 32;
+  while (tmem_cols < 2 * cout) tmem_cols <<= 1;
+
+  for (int b = 0; b < num_blocks; ++b) {
+    const eqt_mix_block& blk = blocks[b];
+    if (blk.dim <= 0 || blk.dim > TILE_M || blk.paths <= 0) return fail(EQT_ERR_BAD_ARGUMENT, "bad block %d", b);
+    const int64_t K = (int64_t)blk.paths * cin;
+    MixArgs a{};
+    a.out = out; a.n = n; a.dim = blk.dim; a.npt = std::min<int64_t>(TILE_M / blk.dim, 256);
+    a.kblocks = (int)(K / KB); a.cout = cout; a.D = comps; a.out_row0 = blk.out_row0;
+    a.stages = stages; a.tmem_cols = tmem_cols; a.status = status;
+
+    CUtensorMap map_a, map_bb, map_bs;
+    {
+      cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)blk.dim, (cuuint64_t)n};
+      cuuint64_t strides[2] = {(cuuint64_t)K * 4, (cuuint64_t)rows * cin * 4};
+      cuuint32_t box[3] = {KB, (cuuint32_t)blk.dim, (cuuint32_t)a.npt};
+      if (int rc = make_map(&map_a, s + (int64_t)blk.in_row0 * cin, 3, dims, strides, box)) return rc;
+    }
+    {
+      cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)cout};
+      cuuint64_t strides[1] = {(cuuint64_t)K * 4};
+      cuuint32_t box[2] = {KB, (cuuint32_t)cout};
+      if (int rc = make_map(&map_bb, w_big + blk.w_offset, 2, dims, strides, box)) return rc;
+      if (int rc = make_map(&map_bs, w_small + blk.w_offset, 2, dims, strides, box)) return rc;
+    }
+    const int64_t tiles = ceil_div(n, a.npt);
+    const unsigned grid = (unsigned)std::min<int64_t>(tiles, sm_count());
+    mix_tc_kernel<<<grid, TC_THREADS, smem, st>>>(map_a, map_bb, map_bs, a);
+    if (int rc = check_launch("mix_tc_kernel")) return rc;
+  }
+  return EQT_OK;
+}

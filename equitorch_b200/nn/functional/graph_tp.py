@@ -30,6 +30,7 @@ from ... import _profile
 from ...graph import EdgeGraph
 from ...ops import batched_sparse_dense_op as _ops
 from ...ops.fused_tp_op import TpTable, cg_inner, cg_segment_sum
+from ...ops.mix_tc_op import MixPlan, mix_tc, supported as _tc_supported
 from ...structs import TensorProductInfo
 
 
@@ -37,7 +38,7 @@ class GraphTPPlan:
     """Device tables of one layer for the fused graph kernels (built once per layer and device)."""
 
     def __init__(self, tp_info_forward: TensorProductInfo, tp_info_backward1: TensorProductInfo,
-                 d_in1: int, d_in2: int, d_out: int, device):
+                 d_in1: int, d_in2: int, d_out: int, device, out_dims=None, in1_dims=None):
         f, b1 = tp_info_forward, tp_info_backward1
         self.fwd_table = TpTable(f.info_Mij_fwd, True, d_in1, d_in2, device)
         # backward-1 tables: input1 is the channel-less operand, input2 the incoming gradient
@@ -46,9 +47,15 @@ class GraphTPPlan:
         self.mix_src = b1.info_M_fwd.to(device)
         self.d_in1, self.d_in2, self.d_out = d_in1, d_in2, d_out
         self.device = torch.device(device)
+        # block structure of the two weight steps for the tensor-core GEMM (None: CUDA-core kernel)
+        self.tc_fwd = MixPlan(f.info_M_fwd, out_dims, device) if out_dims is not None else None
+        self.tc_src = MixPlan(b1.info_M_fwd, in1_dims, device) if in1_dims is not None else None
 
 
-def _mix(s: Tensor, w: Tensor, info, mode: str) -> Tensor:
+def _mix(s: Tensor, w: Tensor, info, mode: str, tc: "MixPlan | None" = None) -> Tensor:
+    if (mode == "uv" and tc is not None and tc.regular and s.dtype == torch.float32
+            and _tc_supported(w.shape[-2], w.shape[-1])):
+        return mix_tc(s, w, tc)
     op = _ops.indexed_vecmat_scale_gather if mode == "uv" else _ops.indexed_mul_scale_gather
     return op(s, w, info.scale, info.index1, info.index2, info.seg_out, out_size=info.out_size)
 
@@ -60,7 +67,7 @@ class SO3LinearGraphFunction(Function):
             s = cg_segment_sum(plan.fwd_table, node_x, y, graph.src_by_dst, graph.dst_order, graph.dst_ptr,
                                graph.num_dst)
         with _profile.timed("channel_mix[fwd]"):
-            out = _mix(s, weight, plan.mix_fwd, mode)
+            out = _mix(s, weight, plan.mix_fwd, mode, plan.tc_fwd)
         ctx.save_for_backward(node_x, y, weight, s if weight.requires_grad else None)
         ctx.graph, ctx.plan, ctx.mode = graph, plan, mode
         return out
@@ -100,7 +107,7 @@ class SO3LinearGraphFunction(Function):
                 sx = cg_segment_sum(plan.bwd1_table, grad, y, graph.dst_by_src, graph.src_order, graph.src_ptr,
                                     graph.num_src)
             with _profile.timed("channel_mix[grad_x]"):
-                gx = _mix(sx, wt, plan.mix_src, mode)
+                gx = _mix(sx, wt, plan.mix_src, mode, plan.tc_src)
         return gx, gy, gw, None, None, None
 
 

@@ -28,7 +28,9 @@ class SO3LinearGraph(SO3Linear):
         device = torch.device(device)
         if device not in self._plans:
             self._plans[device] = GraphTPPlan(self.tp_info_forward, self.tp_info_backward1,
-                                              self.irreps_in1_dim, self.irreps_in2_dim, self.irreps_out_dim, device)
+                                              self.irreps_in1_dim, self.irreps_in2_dim, self.irreps_out_dim, device,
+                                              out_dims=[ir.dim for ir in self.irreps_out],
+                                              in1_dims=[ir.dim for ir in self.irreps_in1])
         return self._plans[device]
 
     def _apply(self, fn, *args, **kwargs):

@@ -1,0 +1,102 @@
+"""Weight step (channel mixing with shared weights) on tcgen05 tensor cores: operator layer.
+
+``MixPlan`` analyses the weight-step table of a layer (``info_M_fwd``: one table entry per intermediate
+row, entries of an output component contiguous, ``index2`` = path of the row) and, when it has the
+regular block structure the GEMM formulation needs - every component of an output irrep receives the
+same paths in the same order - records one ``eqt_mix_block`` per irrep.  ``mix_tc`` packs and splits
+the weights (a few small elementwise kernels on at most a few hundred KB) and calls ``eqt_mix_tc``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+from torch import Tensor
+
+from .. import _lib
+from ..structs import SparseProductInfo
+from .fused_tp_op import status_flag
+
+
+class MixPlan:
+    """Block structure of a weight-step table, or ``regular = False`` if it has none."""
+
+    def __init__(self, info: SparseProductInfo, out_dims: Sequence[int], device):
+        self.regular = False
+        self.device = torch.device(device)
+        if info.index1 is not None or info.scale is not None or info.index2 is None or info.gather_index is not None:
+            return
+        w = info.index2.cpu().numpy()
+        n_out = info.out_size
+        seg = info.seg_out.cpu().numpy() if info.seg_out is not None else np.arange(n_out + 1)
+        if len(seg) != n_out + 1 or sum(out_dims) != n_out or seg[-1] != len(w):
+            return
+        blocks, gather, comp = [], [], 0
+        for dim in out_dims:
+            lists = [tuple(w[seg[comp + m]:seg[comp + m + 1]]) for m in range(dim)]
+            if len(set(lists)) != 1:
+                return
+            paths = len(lists[0])
+            if paths:
+                blocks.append((int(seg[comp]), comp, dim, paths, len(gather)))
+                gather += list(lists[0])
+            comp += dim
+        self.blocks_host = blocks                  # (in_row0, out_row0, dim, paths, first packed path)
+        self.rows = int(len(w))
+        self.comps = n_out
+        self.path_gather = torch.tensor(gather, dtype=torch.long, device=device)
+        self.regular = len(blocks) > 0 and comp == n_out
+        self._struct_cache = {}
+
+    def structs(self, cin: int, cout: int):
+        key = (cin, cout)
+        if key not in self._struct_cache:
+            arr = (_lib.MixBlockStruct * len(self.blocks_host))()
+            for k, (in0, out0, dim, paths, first) in enumerate(self.blocks_host):
+                arr[k] = _lib.MixBlockStruct(in0, out0, dim, paths, first * cin * cout)
+            self._struct_cache[key] = arr
+        return self._struct_cache[key]
+
+    def pack(self, weight: Tensor):
+        """(P, cin, cout) -> per block (cout, paths*cin) row-major, concatenated; split into big + small."""
+        g = weight.detach().index_select(0, self.path_gather)      # (sum paths, cin, cout)
+        parts = []
+        for in0, out0, dim, paths, first in self.blocks_host:
+            parts.append(g[first:first + paths].permute(2, 0, 1).reshape(-1))
+        packed = torch.cat(parts).contiguous()
+        big = _round_tf32(packed)
+        return big, _round_tf32(packed - big)
+
+
+def _round_tf32(x: Tensor) -> Tensor:
+    """Round to the nearest value with 10 mantissa bits (ties away from zero, like ``cvt.rna.tf32.f32``)."""
+    return ((x.view(torch.int32) + 0x1000) & -8192).view(torch.float32)
+
+
+def supported(cin: int, cout: int) -> bool:
+    return cin % 32 == 0 and cout % 16 == 0 and cout <= 256
+
+
+def mix_tc(s: Tensor, weight: Tensor, plan: MixPlan) -> Tensor:
+    """``out[n, M, :] = sum_{rows r of M} s[n, r, :] @ weight[path(r)]`` with float32 accuracy."""
+    dev = _lib.require_cuda(s, weight)
+    assert s.dtype == torch.float32 and weight.dtype == torch.float32 and plan.regular
+    s = s.contiguous()
+    n, rows, cin = s.shape
+    cout = weight.shape[-1]
+    assert rows == plan.rows and weight.shape[-2] == cin
+    big, small = plan.pack(weight)
+    out = torch.zeros(n, plan.comps, cout, dtype=torch.float32, device=dev) if _has_empty(plan) else \
+        torch.empty(n, plan.comps, cout, dtype=torch.float32, device=dev)
+    blocks = plan.structs(cin, cout)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().eqt_mix_tc(s.data_ptr(), big.data_ptr(), small.data_ptr(), out.data_ptr(), n, rows,
+                                         plan.comps, cin, cout, blocks, len(blocks), status_flag(dev).data_ptr(),
+                                         _lib.stream_ptr(dev)), "eqt_mix_tc")
+    return out
+
+
+def _has_empty(plan: MixPlan) -> bool:
+    return sum(b[2] for b in plan.blocks_host) != plan.comps

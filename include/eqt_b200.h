@@ -176,6 +176,31 @@ int eqt_tp_cg_inner(const eqt_tp_table* table, const float* feat, const int64_t*
                     const int64_t* seg_ptr, const int64_t* edge_node, const int64_t* y_index, float* grad_y,
                     int64_t num_nodes, int64_t num_edges, int32_t channels, int32_t* status, void* stream);
 
+/*
+ * Weight step of a layer with weights shared by all samples, on tensor cores (float32 in and out,
+ * 3xTF32 split arithmetic, accumulation in float32):
+ *   out[i, out_row0 + m, co] = sum_{p < paths} sum_ci s[i, in_row0 + m*paths + p, ci] * W_p[ci, co]
+ * for every block (= output irrep) and m < dim.  s (n, rows, cin), out (n, comps, cout).  The
+ * weights of a block are passed packed and split: w_big / w_small + w_offset point to a (cout, paths*cin)
+ * row-major matrix Bt[co, p*cin + ci] = W_p[ci, co], with w_big = W rounded to TF32 (10 mantissa
+ * bits) and w_small = (W - w_big) rounded to TF32.  `blocks` is a host array.  Needs cin % 32 == 0, cout % 16 == 0,
+ * cout <= 256 and 16-byte aligned pointers, else EQT_ERR_UNSUPPORTED (callers then use
+ * eqt_sparse_product with EQT_OP_VECMAT).  `status` is set to 2 if a bounded wait expired.
+ * replaces: indexed_vecmat_scale_gather (equitorch/ops/batched_sparse_dense_op.py:1511) as called by
+ *   sparse_vecmat on the `info_M_fwd` table (equitorch/nn/functional/linears.py:263).
+ */
+typedef struct eqt_mix_block {
+  int32_t in_row0;    /* first intermediate row of the block (its dim*paths rows are contiguous) */
+  int32_t out_row0;   /* first output component of the block                                     */
+  int32_t dim;        /* components of the output irrep (<= 128)                                  */
+  int32_t paths;      /* paths coupling into it                                                   */
+  int64_t w_offset;   /* offset in floats of the block's packed weights                           */
+} eqt_mix_block;
+
+int eqt_mix_tc(const float* s, const float* w_big, const float* w_small, float* out, int64_t n, int32_t rows,
+               int32_t comps, int32_t cin, int32_t cout, const eqt_mix_block* blocks, int32_t num_blocks,
+               int32_t* status, void* stream);
+
 /* Library / device facts. */
 const char* eqt_last_error(void);
 int eqt_version(void);

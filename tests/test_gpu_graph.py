@@ -68,7 +68,8 @@ def test_fused_graph_layer_equals_per_edge_layer_plus_scatter():
     msg = plain(x[src.to(DEV)], y)
     want = torch.zeros_like(out).index_add_(0, dst.to(DEV), msg)
     check_status()
-    torch.testing.assert_close(out, want, rtol=2e-5, atol=2e-5)
+    err = float((out - want).abs().max() / want.abs().max())
+    assert err < 1e-5, f"relative error {err:.2e}"
 
 
 def test_fused_graph_layer_no_edges_and_rectangular():
@@ -89,7 +90,7 @@ def test_fused_graph_layer_no_edges_and_rectangular():
     plain.load_state_dict(layer.state_dict())
     want = torch.zeros(3, 9, c, device=DEV).index_add_(0, dst, plain(x[src], y))
     check_status()
-    torch.testing.assert_close(out, want, rtol=2e-5, atol=2e-5)
+    assert float((out - want).abs().max() / want.abs().max()) < 1e-5
 
 
 def test_large_graph_properties():
