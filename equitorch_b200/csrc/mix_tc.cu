@@ -42,14 +42,13 @@ constexpr int TILE_M = 128;
 constexpr int TC_WAIT_SPINS = 1 << 21;
 
 struct MixArgs {
-  float* out;          // (n, D, cout)
+  float* out;          // first output element of (node 0, m 0)
+  int64_t out_node_stride, out_m_stride;   // in floats; a row holds `cout` contiguous floats
   int64_t n;           // nodes
   int dim;             // components of the output irrep
   int npt;             // nodes per tile (npt * dim <= 128)
   int kblocks;         // K / 32
   int cout;            // N
-  int D;               // components per node in `out`
-  int out_row0;        // first component of this block in `out`
   int stages;
   int tmem_cols;       // power of two >= 2 * cout
   int* status;
@@ -195,24 +194,26 @@ int sm_count() {
 }  // namespace
 }  // namespace eqt
 
-extern "C" int eqt_mix_tc(const float* s, const float* w_big, const float* w_small, float* out, int64_t n,
-                          int32_t rows, int32_t comps, int32_t cin, int32_t cout, const eqt_mix_block* blocks,
-                          int32_t num_blocks, int32_t* status, void* stream) {
-  using namespace eqt;
-  if (n < 0 || rows <= 0 || comps <= 0 || cin <= 0 || cout <= 0 || num_blocks < 0) return fail(EQT_ERR_BAD_ARGUMENT, "bad sizes");
-  if (n == 0 || num_blocks == 0) return EQT_OK;
-  if (!s || !w_big || !w_small || !out || !blocks || !status) return fail(EQT_ERR_BAD_ARGUMENT, "NULL pointer");
-  if (cin % KB != 0 || cout % 16 != 0 || cout > 256) return fail(EQT_ERR_UNSUPPORTED, "tensor-core mix needs C_in %% 32 == 0 and C_out %% 16 == 0, C_out <= 256");
-  if ((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(w_big) | reinterpret_cast<uintptr_t>(w_small) |
-       reinterpret_cast<uintptr_t>(out)) & 15u)
-    return fail(EQT_ERR_UNSUPPORTED, "tensor-core mix needs 16-byte aligned operands");
-  if (n * 1ll > 0x7fffffffll) return fail(EQT_ERR_UNSUPPORTED, "too many nodes for one TMA coordinate");
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
+namespace eqt {
+namespace {
 
-  const uint32_t a_bytes = TILE_M * KB * 4, b_bytes = (uint32_t)cout * KB * 4;
+struct GemmJob {
+  const float* a;            // first element of (node 0, m 0, k 0)
+  int64_t K;                 // reduction length (multiple of 32); row (node, m) holds K contiguous floats
+  int dim;                   // rows per node
+  int64_t a_m_stride, a_node_stride;       // floats
+  const float* b_big;        // (N, K) row-major
+  const float* b_small;
+  int N;                     // multiple of 16, <= 256
+  float* out;
+  int64_t out_node_stride, out_m_stride;   // floats
+};
+
+int launch_job(const GemmJob& j, int64_t n, int* status, cudaStream_t st) {
+  const uint32_t a_bytes = TILE_M * KB * 4, b_bytes = (uint32_t)j.N * KB * 4;
   const uint32_t stage_bytes = 2 * a_bytes + 2 * b_bytes;
-  int stages = (int)std::min<size_t>(8, (220 * 1024 - 1024) / stage_bytes);
-  if (stages < 2) return fail(EQT_ERR_UNSUPPORTED, "C_out too large for the shared-memory ring");
+  const int stages = (int)std::min<size_t>(8, (220 * 1024 - 1024) / stage_bytes);
+  if (stages < 2) return fail(EQT_ERR_UNSUPPORTED, "tile too wide for the shared-memory ring");
   const size_t smem = (size_t)stages * stage_bytes + 1024;
   static bool configured = false;
   if (!configured) {
@@ -220,36 +221,91 @@ extern "C" int eqt_mix_tc(const float* s, const float* w_big, const float* w_sma
     if (e != cudaSuccess) return fail(EQT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     configured = true;
   }
-  int tmem_cols = 32;
-  while (tmem_cols < 2 * cout) tmem_cols <<= 1;
+  MixArgs a{};
+  a.out = j.out; a.out_node_stride = j.out_node_stride; a.out_m_stride = j.out_m_stride;
+  a.n = n; a.dim = j.dim; a.npt = TILE_M / j.dim; a.kblocks = (int)(j.K / KB); a.cout = j.N;
+  a.stages = stages; a.status = status;
+  a.tmem_cols = 32;
+  while (a.tmem_cols < 2 * j.N) a.tmem_cols <<= 1;
+  CUtensorMap map_a, map_bb, map_bs;
+  {
+    cuuint64_t dims[3] = {(cuuint64_t)j.K, (cuuint64_t)j.dim, (cuuint64_t)n};
+    cuuint64_t strides[2] = {(cuuint64_t)j.a_m_stride * 4, (cuuint64_t)j.a_node_stride * 4};
+    cuuint32_t box[3] = {KB, (cuuint32_t)j.dim, (cuuint32_t)a.npt};
+    if (int rc = make_map(&map_a, j.a, 3, dims, strides, box)) return rc;
+  }
+  {
+    cuuint64_t dims[2] = {(cuuint64_t)j.K, (cuuint64_t)j.N};
+    cuuint64_t strides[1] = {(cuuint64_t)j.K * 4};
+    cuuint32_t box[2] = {KB, (cuuint32_t)j.N};
+    if (int rc = make_map(&map_bb, j.b_big, 2, dims, strides, box)) return rc;
+    if (int rc = make_map(&map_bs, j.b_small, 2, dims, strides, box)) return rc;
+  }
+  const int64_t tiles = ceil_div(n, a.npt);
+  const unsigned grid = (unsigned)std::min<int64_t>(tiles, sm_count());
+  mix_tc_kernel<<<grid, TC_THREADS, smem, st>>>(map_a, map_bb, map_bs, a);
+  return check_launch("mix_tc_kernel");
+}
 
+int check_common(const void* a, const void* b, const void* c, const void* d, const eqt_mix_block* blocks, int32_t* status,
+                 int64_t n, int32_t rows, int32_t comps, int32_t cin, int32_t cout, int32_t num_blocks) {
+  if (n < 0 || rows <= 0 || comps <= 0 || cin <= 0 || cout <= 0 || num_blocks < 0) return fail(EQT_ERR_BAD_ARGUMENT, "bad sizes");
+  if (n == 0 || num_blocks == 0) return -1;
+  if (!a || !b || !c || !d || !blocks || !status) return fail(EQT_ERR_BAD_ARGUMENT, "NULL pointer");
+  if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c) |
+       reinterpret_cast<uintptr_t>(d)) & 15u)
+    return fail(EQT_ERR_UNSUPPORTED, "tensor-core mix needs 16-byte aligned operands");
+  if (n > 0x7fffffffll) return fail(EQT_ERR_UNSUPPORTED, "too many nodes for one TMA coordinate");
+  return EQT_OK;
+}
+
+}  // namespace
+}  // namespace eqt
+
+extern "C" int eqt_mix_tc(const float* s, const float* w_big, const float* w_small, float* out, int64_t n,
+                          int32_t rows, int32_t comps, int32_t cin, int32_t cout, const eqt_mix_block* blocks,
+                          int32_t num_blocks, int32_t* status, void* stream) {
+  using namespace eqt;
+  if (int rc = check_common(s, w_big, w_small, out, blocks, status, n, rows, comps, cin, cout, num_blocks))
+    return rc < 0 ? EQT_OK : rc;
+  if (cin % KB != 0 || cout % 16 != 0 || cout > 256)
+    return fail(EQT_ERR_UNSUPPORTED, "tensor-core mix needs C_in %% 32 == 0 and C_out %% 16 == 0, C_out <= 256");
   for (int b = 0; b < num_blocks; ++b) {
     const eqt_mix_block& blk = blocks[b];
     if (blk.dim <= 0 || blk.dim > TILE_M || blk.paths <= 0) return fail(EQT_ERR_BAD_ARGUMENT, "bad block %d", b);
-    const int64_t K = (int64_t)blk.paths * cin;
-    MixArgs a{};
-    a.out = out; a.n = n; a.dim = blk.dim; a.npt = std::min<int64_t>(TILE_M / blk.dim, 256);
-    a.kblocks = (int)(K / KB); a.cout = cout; a.D = comps; a.out_row0 = blk.out_row0;
-    a.stages = stages; a.tmem_cols = tmem_cols; a.status = status;
+    GemmJob j{};
+    j.K = (int64_t)blk.paths * cin; j.dim = blk.dim;
+    j.a = s + (int64_t)blk.in_row0 * cin; j.a_m_stride = j.K; j.a_node_stride = (int64_t)rows * cin;
+    j.b_big = w_big + blk.w_offset; j.b_small = w_small + blk.w_offset; j.N = cout;
+    j.out = out + (int64_t)blk.out_row0 * cout; j.out_node_stride = (int64_t)comps * cout; j.out_m_stride = cout;
+    if (int rc = launch_job(j, n, status, static_cast<cudaStream_t>(stream))) return rc;
+  }
+  return EQT_OK;
+}
 
-    CUtensorMap map_a, map_bb, map_bs;
-    {
-      cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)blk.dim, (cuuint64_t)n};
-      cuuint64_t strides[2] = {(cuuint64_t)K * 4, (cuuint64_t)rows * cin * 4};
-      cuuint32_t box[3] = {KB, (cuuint32_t)blk.dim, (cuuint32_t)a.npt};
-      if (int rc = make_map(&map_a, s + (int64_t)blk.in_row0 * cin, 3, dims, strides, box)) return rc;
+extern "C" int eqt_mix_tc_transposed(const float* g, const float* w_big, const float* w_small, float* g_inter,
+                                     int64_t n, int32_t rows, int32_t comps, int32_t cin, int32_t cout,
+                                     const eqt_mix_block* blocks, int32_t num_blocks, int32_t* status, void* stream) {
+  using namespace eqt;
+  if (int rc = check_common(g, w_big, w_small, g_inter, blocks, status, n, rows, comps, cin, cout, num_blocks))
+    return rc < 0 ? EQT_OK : rc;
+  if (cout % KB != 0 || cin % 16 != 0)
+    return fail(EQT_ERR_UNSUPPORTED, "transposed tensor-core mix needs C_out %% 32 == 0 and C_in %% 16 == 0");
+  for (int b = 0; b < num_blocks; ++b) {
+    const eqt_mix_block& blk = blocks[b];
+    if (blk.dim <= 0 || blk.dim > TILE_M || blk.paths <= 0) return fail(EQT_ERR_BAD_ARGUMENT, "bad block %d", b);
+    const int64_t width = (int64_t)blk.paths * cin;        // floats per (node, m) row of g_inter
+    const int chunk_max = (256 / cin) > 0 ? (256 / cin) * cin : 0;
+    if (chunk_max == 0) return fail(EQT_ERR_UNSUPPORTED, "C_in > 256");
+    for (int64_t c0 = 0; c0 < width; c0 += chunk_max) {
+      GemmJob j{};
+      j.K = cout; j.dim = blk.dim;
+      j.a = g + (int64_t)blk.out_row0 * cout; j.a_m_stride = cout; j.a_node_stride = (int64_t)comps * cout;
+      j.b_big = w_big + blk.w_offset + c0 * cout; j.b_small = w_small + blk.w_offset + c0 * cout;
+      j.N = (int)std::min<int64_t>(chunk_max, width - c0);
+      j.out = g_inter + (int64_t)blk.in_row0 * cin + c0; j.out_node_stride = (int64_t)rows * cin; j.out_m_stride = width;
+      if (int rc = launch_job(j, n, status, static_cast<cudaStream_t>(stream))) return rc;
     }
-    {
-      cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)cout};
-      cuuint64_t strides[1] = {(cuuint64_t)K * 4};
-      cuuint32_t box[2] = {KB, (cuuint32_t)cout};
-      if (int rc = make_map(&map_bb, w_big + blk.w_offset, 2, dims, strides, box)) return rc;
-      if (int rc = make_map(&map_bs, w_small + blk.w_offset, 2, dims, strides, box)) return rc;
-    }
-    const int64_t tiles = ceil_div(n, a.npt);
-    const unsigned grid = (unsigned)std::min<int64_t>(tiles, sm_count());
-    mix_tc_kernel<<<grid, TC_THREADS, smem, st>>>(map_a, map_bb, map_bs, a);
-    if (int rc = check_launch("mix_tc_kernel")) return rc;
   }
   return EQT_OK;
 }

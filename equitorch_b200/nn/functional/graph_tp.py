@@ -30,7 +30,8 @@ from ... import _profile
 from ...graph import EdgeGraph
 from ...ops import batched_sparse_dense_op as _ops
 from ...ops.fused_tp_op import TpTable, cg_inner, cg_segment_sum
-from ...ops.mix_tc_op import MixPlan, mix_tc, supported as _tc_supported
+from ...ops.mix_tc_op import (MixPlan, mix_tc, mix_tc_transposed, supported as _tc_supported,
+                              supported_transposed as _tc_supported_t)
 from ...structs import TensorProductInfo
 
 
@@ -93,7 +94,11 @@ class SO3LinearGraphFunction(Function):
         if ctx.needs_input_grad[1]:
             # gradient w.r.t. the node-level intermediate: G[d, r] = g[d, M(r)] W[w(r)]^T
             with _profile.timed("channel_mix[grad_inter]"):
-                if mode == "uv":
+                tc = plan.tc_fwd
+                if (mode == "uv" and tc is not None and tc.regular
+                        and _tc_supported_t(weight.shape[-2], weight.shape[-1])):
+                    g_inter = mix_tc_transposed(grad, weight, tc)
+                elif mode == "uv":
                     g_inter = _ops.indexed_vecmat_scale_gather(grad, wt, b1.scale, b1.index2, b1.index1, b1.seg_out,
                                                                out_size=b1.out_size)
                 else:

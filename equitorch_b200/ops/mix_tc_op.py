@@ -70,6 +70,31 @@ class MixPlan:
         return big, _round_tf32(packed - big)
 
 
+def mix_tc_transposed(g: Tensor, weight: Tensor, plan: MixPlan) -> Tensor:
+    """Gradient of :func:`mix_tc` w.r.t. its first argument: ``g_inter[n, r, :] = g[n, M(r), :] @ weight[path(r)]^T``."""
+    dev = _lib.require_cuda(g, weight)
+    assert g.dtype == torch.float32 and weight.dtype == torch.float32 and plan.regular
+    g = g.contiguous()
+    n, comps, cout = g.shape
+    cin = weight.shape[-2]
+    assert comps == plan.comps and weight.shape[-1] == cout
+    stacked = weight.detach().index_select(0, plan.path_gather).reshape(-1)     # blocks are contiguous runs of paths
+    big = _round_tf32(stacked)
+    small = _round_tf32(stacked - big)
+    out = torch.empty(n, plan.rows, cin, dtype=torch.float32, device=dev)
+    blocks = plan.structs(cin, cout)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().eqt_mix_tc_transposed(g.data_ptr(), big.data_ptr(), small.data_ptr(), out.data_ptr(), n,
+                                                    plan.rows, comps, cin, cout, blocks, len(blocks),
+                                                    status_flag(dev).data_ptr(), _lib.stream_ptr(dev)),
+                   "eqt_mix_tc_transposed")
+    return out
+
+
+def supported_transposed(cin: int, cout: int) -> bool:
+    return cout % 32 == 0 and cin % 16 == 0 and cin <= 256
+
+
 def _round_tf32(x: Tensor) -> Tensor:
     """Round to the nearest value with 10 mantissa bits (ties away from zero, like ``cvt.rna.tf32.f32``)."""
     return ((x.view(torch.int32) + 0x1000) & -8192).view(torch.float32)

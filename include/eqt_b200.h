@@ -201,6 +201,20 @@ int eqt_mix_tc(const float* s, const float* w_big, const float* w_small, float* 
                int32_t comps, int32_t cin, int32_t cout, const eqt_mix_block* blocks, int32_t num_blocks,
                int32_t* status, void* stream);
 
+/*
+ * Adjoint of the weight step with respect to the intermediate, same arithmetic:
+ *   g_inter[i, in_row0 + m*paths + p, ci] = sum_co g[i, out_row0 + m, co] * W_p[ci, co]
+ * g (n, comps, cout), g_inter (n, rows, cin).  Here w_big / w_small + w_offset point to the block's
+ * (paths*cin, cout) row-major matrix B[p*cin + ci, co] = W_p[ci, co] (the weights of the block's paths
+ * stacked, no transpose), split like above; w_offset is in floats as before (paths*cin*cout per block).
+ * Needs cout % 32 == 0, cin % 16 == 0, cin <= 256.
+ * replaces: indexed_mat_t_vec_scale_gather on the `info_M_bwd1` table, the gradient of sparse_vecmat
+ *   with respect to its vector input (equitorch/nn/functional/sparse_product.py:268-270).
+ */
+int eqt_mix_tc_transposed(const float* g, const float* w_big, const float* w_small, float* g_inter, int64_t n,
+                          int32_t rows, int32_t comps, int32_t cin, int32_t cout, const eqt_mix_block* blocks,
+                          int32_t num_blocks, int32_t* status, void* stream);
+
 /* Library / device facts. */
 const char* eqt_last_error(void);
 int eqt_version(void);

@@ -5,7 +5,7 @@ import torch
 from equitorch_b200.irreps import Irreps
 from equitorch_b200.ops import batched_sparse_dense_op as gops
 from equitorch_b200.ops.fused_tp_op import check_status
-from equitorch_b200.ops.mix_tc_op import MixPlan, mix_tc
+from equitorch_b200.ops.mix_tc_op import MixPlan, mix_tc, mix_tc_transposed
 from equitorch_b200.tables import tp_infos
 
 pytestmark = pytest.mark.gpu
@@ -38,3 +38,22 @@ def test_mix_tc_matches_float64(irreps, n, cin, cout):
     # the float32 accumulation inside the tensor core is not round-to-nearest: a few 1e-6 of the largest
     # element is what the hardware gives; the parity bar for float32 results is 1e-5
     assert err_tc < 8e-6, f"tensor-core path: relative error {err_tc:.2e} (CUDA-core path {err_simt:.2e})"
+
+
+@pytest.mark.parametrize("irreps,n,cin,cout", [("0e+1o+2e+3o", 1000, 64, 64), ("0e+1o+2e", 77, 48, 32),
+                                               ("0e+1o+2e+3o", 20011, 64, 64)])
+def test_mix_tc_transposed_is_the_adjoint(irreps, n, cin, cout):
+    ir = Irreps(irreps)
+    fwd, _, _, paths = tp_infos(ir, ir, Irreps("0e+1o+2e+3o"))
+    info = fwd.info_M_fwd.to(DEV)
+    plan = MixPlan(info, [i.dim for i in ir], DEV)
+    gen = torch.Generator().manual_seed(n + 1)
+    g = torch.randn(n, plan.comps, cout, generator=gen).to(DEV)
+    w = (torch.randn(paths, cin, cout, generator=gen) / cout ** 0.5).to(DEV)
+    got = mix_tc_transposed(g, w, plan)
+    check_status()
+    seg = info.seg_out.cpu() if info.seg_out is not None else torch.arange(info.out_size + 1)
+    comp_of_row = torch.repeat_interleave(torch.arange(info.out_size), seg[1:] - seg[:-1]).to(DEV)
+    want = torch.einsum("nro,rio->nri", g.double()[:, comp_of_row], w.double()[info.index2])
+    err = float((got.double() - want).abs().max() / want.abs().max())
+    assert got.shape == want.shape and err < 8e-6, f"relative error {err:.2e}"
