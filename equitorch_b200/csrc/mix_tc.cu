@@ -144,6 +144,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
 }  // namespace eqt
 
 #include "mix_tc_kernel.inc"
+#include "wgrad_tc_kernel.inc"
 
 // ------------------------------------------------------------------------------------------
 // host side
@@ -169,12 +170,12 @@ EncodeTiledFn encode_tiled() {
 }
 
 int make_map(CUtensorMap* map, const float* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides_bytes,
-             const cuuint32_t* box) {
+             const cuuint32_t* box, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn enc = encode_tiled();
   if (!enc) return fail(EQT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint32_t ones[3] = {1, 1, 1};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<float*>(base), dims,
-                   strides_bytes, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   strides_bytes, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(EQT_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   return EQT_OK;
@@ -306,6 +307,72 @@ extern "C" int eqt_mix_tc_transposed(const float* g, const float* w_big, const f
       j.out = g_inter + (int64_t)blk.in_row0 * cin + c0; j.out_node_stride = (int64_t)rows * cin; j.out_m_stride = width;
       if (int rc = launch_job(j, n, status, static_cast<cudaStream_t>(stream))) return rc;
     }
+  }
+  return EQT_OK;
+}
+
+extern "C" int eqt_wgrad_tc(const float* s, const float* g, float* gw_packed, float* scratch, int64_t scratch_floats,
+                            int64_t n, int32_t rows, int32_t comps, int32_t cin, int32_t cout,
+                            const eqt_mix_block* blocks, int32_t num_blocks, int32_t* status, void* stream) {
+  using namespace eqt;
+  if (int rc = check_common(s, g, gw_packed, scratch, blocks, status, n, rows, comps, cin, cout, num_blocks))
+    return rc < 0 ? EQT_OK : rc;
+  if (cin % 32 != 0 || cout % 32 != 0 || cout > 128)
+    return fail(EQT_ERR_UNSUPPORTED, "tensor-core weight gradient needs C_in %% 32 == 0, C_out %% 32 == 0, C_out <= 128");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(wgrad_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    if (e != cudaSuccess) return fail(EQT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  const int b_boxes = cout / 32;
+  const size_t budget = 220 * 1024 - 1024;
+  for (int b = 0; b < num_blocks; ++b) {
+    const eqt_mix_block& blk = blocks[b];
+    if (blk.dim <= 0 || blk.dim > TILE_M || blk.paths <= 0) return fail(EQT_ERR_BAD_ARGUMENT, "bad block %d", b);
+    const int64_t K = (int64_t)blk.paths * cin;                 // M extent of this GEMM
+    const int m_tiles = (int)ceil_div(K, 128);
+    // reduction rows per tile: multiple of 8 and of dim, two stages must fit in shared memory
+    const size_t bytes_per_row = 2 * (size_t)(4 + b_boxes) * 128;
+    int rows_cap = (int)std::min<size_t>(128, budget / 2 / bytes_per_row);
+    int step = 8;
+    for (int d = blk.dim; d % 2 == 0 && step > 1; d /= 2) step /= 2;   // 8 / gcd(dim, 8)
+    const int npt = (rows_cap / blk.dim) / step * step;
+    if (npt <= 0) return fail(EQT_ERR_UNSUPPORTED, "irrep with %d components does not fit a reduction tile", blk.dim);
+    WgradArgs a{};
+    a.n = n; a.dim = blk.dim; a.npt = npt; a.n_cols = cout; a.status = status;
+    const size_t stage_bytes = bytes_per_row * (size_t)(npt * blk.dim);
+    a.stages = (int)std::min<size_t>(4, budget / stage_bytes);
+    a.tmem_cols = 32;
+    while (a.tmem_cols < 2 * cout) a.tmem_cols <<= 1;
+    a.chunk_tiles = std::max(1, 512 / (npt * blk.dim));
+    const int64_t tiles = ceil_div(n, npt);
+    const int splits = (int)std::max<int64_t>(1, std::min<int64_t>(tiles, sm_count() / m_tiles));
+    const int64_t need = (int64_t)splits * m_tiles * 128 * cout;
+    if (need > scratch_floats) return fail(EQT_ERR_BAD_ARGUMENT, "scratch too small: %lld floats needed", (long long)need);
+    a.partial = scratch;
+    CUtensorMap map_s, map_g;
+    {
+      cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)blk.dim, (cuuint64_t)n};
+      cuuint64_t strides[2] = {(cuuint64_t)K * 4, (cuuint64_t)rows * cin * 4};
+      cuuint32_t box[3] = {KB, (cuuint32_t)blk.dim, (cuuint32_t)npt};
+      if (int rc = make_map(&map_s, s + (int64_t)blk.in_row0 * cin, 3, dims, strides, box,
+                            CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return rc;
+    }
+    {
+      cuuint64_t dims[3] = {(cuuint64_t)cout, (cuuint64_t)blk.dim, (cuuint64_t)n};
+      cuuint64_t strides[2] = {(cuuint64_t)cout * 4, (cuuint64_t)comps * cout * 4};
+      cuuint32_t box[3] = {KB, (cuuint32_t)blk.dim, (cuuint32_t)npt};
+      if (int rc = make_map(&map_g, g + (int64_t)blk.out_row0 * cout, 3, dims, strides, box,
+                            CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return rc;
+    }
+    dim3 grid((unsigned)splits, (unsigned)m_tiles);
+    wgrad_tc_kernel<<<grid, TC_THREADS, (size_t)a.stages * stage_bytes + 1024, st>>>(map_s, map_g, a);
+    if (int rc = check_launch("wgrad_tc_kernel")) return rc;
+    wgrad_reduce_kernel<<<flat_grid(K * cout / 4, 256), 256, 0, st>>>(scratch, gw_packed + blk.w_offset, splits,
+                                                                      (int64_t)m_tiles * 128, K, cout);
+    if (int rc = check_launch("wgrad_reduce_kernel")) return rc;
   }
   return EQT_OK;
 }

@@ -30,8 +30,8 @@ from ... import _profile
 from ...graph import EdgeGraph
 from ...ops import batched_sparse_dense_op as _ops
 from ...ops.fused_tp_op import TpTable, cg_inner, cg_segment_sum
-from ...ops.mix_tc_op import (MixPlan, mix_tc, mix_tc_transposed, supported as _tc_supported,
-                              supported_transposed as _tc_supported_t)
+from ...ops.mix_tc_op import (MixPlan, mix_tc, mix_tc_transposed, wgrad_tc, supported as _tc_supported,
+                              supported_transposed as _tc_supported_t, supported_wgrad as _tc_supported_w)
 from ...structs import TensorProductInfo
 
 
@@ -84,7 +84,11 @@ class SO3LinearGraphFunction(Function):
         wt = weight.transpose(-1, -2).contiguous() if mode == "uv" else weight
         if ctx.needs_input_grad[2]:
             with _profile.timed("weight_grad"):
-                if mode == "uv":   # (P, Cout, Cin) summed over nodes, then transposed to the weight's layout
+                tcw = plan.tc_fwd
+                if (mode == "uv" and tcw is not None and tcw.regular and grad.dtype == torch.float32
+                        and _tc_supported_w(weight.shape[-2], weight.shape[-1])):
+                    gw = wgrad_tc(s, grad, tcw, weight.shape[0])
+                elif mode == "uv":   # (P, Cout, Cin) summed over nodes, then transposed to the weight's layout
                     gw = _ops.indexed_outer_scale_gather(grad, s, b2.scale, b2.index1, b2.index2, b2.seg_out,
                                                          out_accumulated=True, out_size=b2.out_size)
                     gw = gw.transpose(-1, -2).contiguous()

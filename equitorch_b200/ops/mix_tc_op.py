@@ -91,6 +91,44 @@ def mix_tc_transposed(g: Tensor, weight: Tensor, plan: MixPlan) -> Tensor:
     return out
 
 
+_scratch = {}
+
+
+def wgrad_scratch(device, cout: int) -> Tensor:
+    """Per-device scratch for the split reduction of :func:`wgrad_tc` (128 * cout floats per SM)."""
+    device = torch.device(device)
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    need = 128 * cout * sms
+    buf = _scratch.get(device)
+    if buf is None or buf.numel() < need:
+        buf = torch.empty(need, dtype=torch.float32, device=device)
+        _scratch[device] = buf
+    return buf
+
+
+def wgrad_tc(s: Tensor, g: Tensor, plan: MixPlan, num_paths: int) -> Tensor:
+    """``gw[p] = sum_n sum_{rows r of path p} s[n, r, :]^T g[n, M(r), :]`` -> (num_paths, cin, cout), deterministic."""
+    dev = _lib.require_cuda(s, g)
+    assert s.dtype == torch.float32 and g.dtype == torch.float32 and plan.regular
+    s, g = s.contiguous(), g.contiguous()
+    n, rows, cin = s.shape
+    cout = g.shape[-1]
+    packed = torch.empty(plan.path_gather.numel(), cin, cout, dtype=torch.float32, device=dev)
+    scratch = wgrad_scratch(dev, cout)
+    blocks = plan.structs(cin, cout)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().eqt_wgrad_tc(s.data_ptr(), g.data_ptr(), packed.data_ptr(), scratch.data_ptr(),
+                                           scratch.numel(), n, rows, plan.comps, cin, cout, blocks, len(blocks),
+                                           status_flag(dev).data_ptr(), _lib.stream_ptr(dev)), "eqt_wgrad_tc")
+    if plan.path_gather.numel() == num_paths and bool((plan.path_gather == torch.arange(num_paths, device=dev)).all()):
+        return packed
+    return torch.zeros(num_paths, cin, cout, dtype=torch.float32, device=dev).index_add_(0, plan.path_gather, packed)
+
+
+def supported_wgrad(cin: int, cout: int) -> bool:
+    return cin % 32 == 0 and cout % 32 == 0 and cout <= 128
+
+
 def supported_transposed(cin: int, cout: int) -> bool:
     return cout % 32 == 0 and cin % 16 == 0 and cin <= 256
 

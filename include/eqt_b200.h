@@ -215,6 +215,21 @@ int eqt_mix_tc_transposed(const float* g, const float* w_big, const float* w_sma
                           int32_t rows, int32_t comps, int32_t cin, int32_t cout, const eqt_mix_block* blocks,
                           int32_t num_blocks, int32_t* status, void* stream);
 
+/*
+ * Gradient of the weight step with respect to weights shared by all samples, on tensor cores:
+ *   gw_packed[w_offset + (p*cin + ci)*cout + co] = sum_i sum_m s[i, in_row0 + m*paths + p, ci] * g[i, out_row0 + m, co]
+ * i.e. per block a (paths*cin, cout) row-major matrix, the same stacking as the weights handed to
+ * eqt_mix_tc_transposed.  The sum over the n samples is split over CTAs; their float32 partial sums go
+ * through `scratch` (at least 128 * cout * #SMs floats, caller-owned, contents undefined afterwards)
+ * and are reduced in a fixed order: no atomics, results are bit-reproducible.
+ * Needs cin % 32 == 0, cout % 32 == 0, cout <= 128.
+ * replaces: indexed_outer_scale_gather with out_accumulated=True on the `info_M_bwd2` table
+ *   (equitorch/nn/functional/linears.py:316-320), which uses atomic adds in the reference.
+ */
+int eqt_wgrad_tc(const float* s, const float* g, float* gw_packed, float* scratch, int64_t scratch_floats, int64_t n,
+                 int32_t rows, int32_t comps, int32_t cin, int32_t cout, const eqt_mix_block* blocks,
+                 int32_t num_blocks, int32_t* status, void* stream);
+
 /* Library / device facts. */
 const char* eqt_last_error(void);
 int eqt_version(void);

@@ -5,7 +5,7 @@ import torch
 from equitorch_b200.irreps import Irreps
 from equitorch_b200.ops import batched_sparse_dense_op as gops
 from equitorch_b200.ops.fused_tp_op import check_status
-from equitorch_b200.ops.mix_tc_op import MixPlan, mix_tc, mix_tc_transposed
+from equitorch_b200.ops.mix_tc_op import MixPlan, mix_tc, mix_tc_transposed, wgrad_tc
 from equitorch_b200.tables import tp_infos
 
 pytestmark = pytest.mark.gpu
@@ -57,3 +57,25 @@ def test_mix_tc_transposed_is_the_adjoint(irreps, n, cin, cout):
     want = torch.einsum("nro,rio->nri", g.double()[:, comp_of_row], w.double()[info.index2])
     err = float((got.double() - want).abs().max() / want.abs().max())
     assert got.shape == want.shape and err < 8e-6, f"relative error {err:.2e}"
+
+
+@pytest.mark.parametrize("irreps,n,cin,cout", [("0e+1o+2e+3o", 1000, 64, 64), ("0e+1o+2e", 77, 32, 32),
+                                               ("0e+1o+2e+3o", 20011, 64, 64), ("0e+1o+2e+3o", 5, 64, 64)])
+def test_wgrad_tc_matches_float64_and_is_reproducible(irreps, n, cin, cout):
+    ir = Irreps(irreps)
+    fwd, _, _, paths = tp_infos(ir, ir, Irreps("0e+1o+2e+3o"))
+    info = fwd.info_M_fwd.to(DEV)
+    plan = MixPlan(info, [i.dim for i in ir], DEV)
+    gen = torch.Generator().manual_seed(n + 2)
+    s = torch.randn(n, plan.rows, cin, generator=gen).to(DEV)
+    g = torch.randn(n, plan.comps, cout, generator=gen).to(DEV)
+    got = wgrad_tc(s, g, plan, paths)
+    again = wgrad_tc(s, g, plan, paths)
+    check_status()
+    assert torch.equal(got, again)
+    seg = info.seg_out.cpu() if info.seg_out is not None else torch.arange(info.out_size + 1)
+    comp_of_row = torch.repeat_interleave(torch.arange(info.out_size), seg[1:] - seg[:-1]).to(DEV)
+    per_row = torch.einsum("nri,nro->rio", s.double(), g.double()[:, comp_of_row])
+    want = torch.zeros(paths, cin, cout, dtype=torch.float64, device=DEV).index_add_(0, info.index2, per_row)
+    err = float((got.double() - want).abs().max() / want.abs().max())
+    assert err < 8e-6, f"relative error {err:.2e}"
