@@ -376,3 +376,61 @@ extern "C" int eqt_wgrad_tc(const float* s, const float* g, float* gw_packed, fl
   }
   return EQT_OK;
 }
+
+// ------------------------------------------------------------------------------------------
+// Weight gradient without any caller-side or library-side allocation
+// ------------------------------------------------------------------------------------------
+namespace eqt {
+namespace {
+
+// Scratch for the per-CTA partial sums of eqt_wgrad_tc_static: 148 SMs x 128 rows x 64 columns of
+// float32 = 4,849,664 bytes, resident on every GPU that loads this library until the process exits.
+constexpr int64_t kStaticScratchFloats = 148ll * 128 * 64;
+static __device__ __align__(256) float g_wgrad_scratch[kStaticScratchFloats];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+float* g_static_ptr[kMaxDevices] = {};
+
+// Device address of g_wgrad_scratch on the current device.  In host code the symbol itself is only a
+// handle; the address a kernel can use comes from cudaGetSymbolAddress, once per device.
+int static_scratch(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(EQT_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(EQT_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (!g_static_ptr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_wgrad_scratch);
+    if (e != cudaSuccess || !p) return fail(EQT_ERR_CUDA, "cudaGetSymbolAddress(g_wgrad_scratch): %s", cudaGetErrorString(e));
+    g_static_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_static_ptr[dev];
+  return EQT_OK;
+}
+
+}  // namespace
+}  // namespace eqt
+
+extern "C" int64_t eqt_wgrad_tc_static_capacity(void) { return eqt::kStaticScratchFloats; }
+
+extern "C" int eqt_wgrad_tc_static(const float* s, const float* g, float* gw_packed, int64_t n, int32_t rows,
+                                   int32_t comps, int32_t cin, int32_t cout, const eqt_mix_block* blocks,
+                                   int32_t num_blocks, int32_t* status, void* stream) {
+  using namespace eqt;
+  if (cout > 64)
+    return fail(EQT_ERR_UNSUPPORTED,
+                "eqt_wgrad_tc_static: C_out = %d exceeds the limit of 64 output channels of the built-in scratch "
+                "(%lld floats); use eqt_wgrad_tc with a caller-provided scratch buffer", (int)cout,
+                (long long)kStaticScratchFloats);
+  if ((int64_t)sm_count() * 128 * cout > kStaticScratchFloats)
+    return fail(EQT_ERR_UNSUPPORTED,
+                "eqt_wgrad_tc_static: %d SMs x 128 x %d floats exceed the built-in scratch of %lld floats; use "
+                "eqt_wgrad_tc with a caller-provided scratch buffer", sm_count(), (int)cout,
+                (long long)kStaticScratchFloats);
+  float* scratch = nullptr;
+  if (int rc = static_scratch(&scratch)) return rc;
+  return eqt_wgrad_tc(s, g, gw_packed, scratch, kStaticScratchFloats, n, rows, comps, cin, cout, blocks, num_blocks,
+                      status, stream);
+}

@@ -230,6 +230,28 @@ int eqt_wgrad_tc(const float* s, const float* g, float* gw_packed, float* scratc
                  int32_t rows, int32_t comps, int32_t cin, int32_t cout, const eqt_mix_block* blocks,
                  int32_t num_blocks, int32_t* status, void* stream);
 
+/*
+ * eqt_wgrad_tc for callers that cannot hand over a scratch buffer because they cannot allocate device
+ * memory at the point of the call: a C or Fortran host program that links this library without a
+ * CUDA allocator of its own, or a plug-in running inside a framework that reserved all device memory
+ * in its own arena at start-up and forbids cudaMalloc afterwards.  Same arguments and results as
+ * eqt_wgrad_tc minus `scratch`; the per-CTA partial sums go through a 4.85 MB array that is part of the
+ * library image on every GPU (148 x 128 x 64 floats, eqt_wgrad_tc_static_capacity()).  The function
+ * and everything it calls allocate nothing.
+ *   - Limit: cout <= 64 and (#SMs * 128 * cout) floats must fit the array; larger requests return
+ *     EQT_ERR_UNSUPPORTED with a message naming the limit - use eqt_wgrad_tc then.
+ *   - The first call on each device looks up the array's device address (with that device current);
+ *     make that first call outside any stream capture.
+ *   - All calls on a device share the one array.  Nothing in it has to be zero on entry (every partial
+ *     sum that is read back was written by the same call), but two calls whose kernels overlap on the
+ *     GPU (different streams) race on it: serialise them.
+ * No counterpart in the reference: it has no C interface and leaves all allocation to PyTorch.
+ */
+int eqt_wgrad_tc_static(const float* s, const float* g, float* gw_packed, int64_t n, int32_t rows, int32_t comps,
+                        int32_t cin, int32_t cout, const eqt_mix_block* blocks, int32_t num_blocks,
+                        int32_t* status, void* stream);
+int64_t eqt_wgrad_tc_static_capacity(void);
+
 /* Library / device facts. */
 const char* eqt_last_error(void);
 int eqt_version(void);
