@@ -78,25 +78,45 @@ def partition(s: Structure, warps: int = NUM_WARPS):
     return wt, wr
 
 
-def _emit_segsum(s: Structure, wt, wr, w: int) -> List[str]:
+def kernel_order(s: Structure, warps: int = NUM_WARPS) -> np.ndarray:
+    """Order in which the unrolled code visits the table entries (a permutation of ``range(T)``).
+
+    Inside a warp's range the entries are interleaved across rows (first entry of every row, then
+    the second of every row, ...), so that consecutive FMAs hit different accumulators instead of
+    forming one dependent chain per row.  The run-time arrays handed to the unrolled kernels
+    (``scale``, ``m_y``) are stored in this order.
+    """
+    wt, _ = partition(s, warps)
+    order = []
+    for w in range(warps):
+        ts = np.arange(wt[w], wt[w + 1])
+        if len(ts) == 0:
+            continue
+        rows = s.row[ts]
+        pos = ts - np.searchsorted(rows, rows, side="left") - wt[w]      # index of the entry within its row
+        order.append(ts[np.lexsort((rows, pos))])
+    return np.concatenate(order) if order else np.zeros(0, dtype=np.int64)
+
+
+def _emit_segsum(s: Structure, order, wt, wr, w: int) -> List[str]:
     lines = []
     tb, te, rb = wt[w], wt[w + 1], wr[w]
     for q0 in range(tb, te, 4):
         lines.append(f"    c = cf[{(q0 - tb) // 4}];")
-        for t in range(q0, min(q0 + 4, te)):
-            comp = "xyzw"[t - q0]
+        for q in range(q0, min(q0 + 4, te)):
+            comp, t = "xyzw"[q - q0], int(order[q])
             r, m = int(s.row[t]) - rb, int(s.mf[t])
             lines.append(f"    EQT_FMA_ROW(acc[{r}], c.{comp}, x[{m}]);")
     return lines
 
 
-def _emit_inner(s: Structure, wt, wr, w: int) -> List[str]:
+def _emit_inner(s: Structure, order, wt, wr, w: int) -> List[str]:
     lines = []
     tb, te, rb = wt[w], wt[w + 1], wr[w]
     for q0 in range(tb, te, 4):
         lines.append(f"    c = sc[{(q0 - tb) // 4}];")
-        for t in range(q0, min(q0 + 4, te)):
-            comp = "xyzw"[t - q0]
+        for q in range(q0, min(q0 + 4, te)):
+            comp, t = "xyzw"[q - q0], int(order[q])
             r, m, k = int(s.row[t]) - rb, int(s.mf[t]), int(s.my[t])
             lines.append(f"    ay[{k}] = fmaf(c.{comp}, EQT_DOT_ROW(x[{m}], g[{r}]), ay[{k}]);")
     return lines
@@ -104,6 +124,7 @@ def _emit_inner(s: Structure, wt, wr, w: int) -> List[str]:
 
 def emit_spec(idx: int, s: Structure, note: str) -> str:
     wt, wr = partition(s)
+    order = kernel_order(s)
     maxr = max(wr[w + 1] - wr[w] for w in range(NUM_WARPS))
     maxt = max(wt[w + 1] - wt[w] for w in range(NUM_WARPS))
     out = [f"// {note}", f"struct Spec{idx} {{",
@@ -116,12 +137,12 @@ def emit_spec(idx: int, s: Structure, note: str) -> str:
         out.append("  template <int CPL> __device__ __forceinline__ static void "
                    f"segsum_w{w}(float (&acc)[MAXR][CPL], const float (&x)[DF][CPL], const float4* cf) {{")
         out.append("    float4 c;")
-        out += _emit_segsum(s, wt, wr, w)
+        out += _emit_segsum(s, order, wt, wr, w)
         out.append("  }")
         out.append("  template <int CPL> __device__ __forceinline__ static void "
                    f"inner_w{w}(float (&ay)[DY], const float (&x)[DF][CPL], const float (&g)[MAXR][CPL], const float4* sc) {{")
         out.append("    float4 c;")
-        out += _emit_inner(s, wt, wr, w)
+        out += _emit_inner(s, order, wt, wr, w)
         out.append("  }")
     out.append("};")
     return "\n".join(out)

@@ -55,6 +55,8 @@ struct FusedArgs {
   const int64_t* ptr;       // (N + 1) CSR of edges per output node, or NULL (one edge per output)
   const int64_t* enode;     // (E) node of each edge (generic inner kernel only)
   const float* scale;       // (T)
+  const float* scale_k;     // (T) in the unrolled kernels' entry order, or NULL
+  const int64_t* my_k;      // (T) likewise
   const int64_t* mf;        // (T)
   const int64_t* my;        // (T)
   const int64_t* rowptr;    // (R + 1)
@@ -110,7 +112,8 @@ __device__ __forceinline__ void warp_ranges(int w, int& tb, int& te, int& rb, in
 template <class S, int CPL>
 constexpr size_t spec_smem_bytes() {
   return sizeof(float) * (2 * STAGES * S::DF * 32 * CPL   // feature rows, two sets
-                          + NW * S::MAXT                  // per-warp coefficients / scales
+                          + 2 * NW * S::MAXT              // per-warp coefficients and scales
+                          + NW * STAGES * S::DY           // per-warp copy of the batch's harmonics
                           + 2 * STAGES * NW * S::DY)      // inner: per-warp partial grad_y, two sets
          + S::T                                           // my[] as bytes
          + 64;
@@ -120,20 +123,24 @@ constexpr size_t spec_smem_bytes() {
 template <class S, int CPL>
 struct Smem {
   float* xs;
-  float* wbuf;    // [NW][MAXT]
+  float* wbuf;    // [NW][MAXT] coefficients of the current edge
+  float* wsc;     // [NW][MAXT] scales of the warp's entries
+  float* wy;      // [NW][STAGES][DY]
   float* red;     // [2][STAGES][NW][DY]
   uint8_t* smy;   // [T]
   __device__ explicit Smem(unsigned char* base) {
     xs = reinterpret_cast<float*>(base);
     wbuf = xs + 2 * STAGES * S::DF * 32 * CPL;
-    red = wbuf + NW * S::MAXT;
+    wsc = wbuf + NW * S::MAXT;
+    wy = wsc + NW * S::MAXT;
+    red = wy + NW * STAGES * S::DY;
     smy = reinterpret_cast<uint8_t*>(red + 2 * STAGES * NW * S::DY);
   }
 };
 
 // ---- spec kernel: gather + CG + segment sum -----------------------------------------------------
 template <class S, int CPL>
-__global__ void __launch_bounds__(NW * 32) tp_segsum_spec_kernel(FusedArgs a) {
+__global__ void __launch_bounds__(NW * 32, 4) tp_segsum_spec_kernel(FusedArgs a) {
   constexpr int C = 32 * CPL, ROWF = S::DF * C;
   constexpr uint32_t ROWB = ROWF * sizeof(float);
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -143,8 +150,11 @@ __global__ void __launch_bounds__(NW * 32) tp_segsum_spec_kernel(FusedArgs a) {
   int tb, te, rb, re;
   warp_ranges<S>(warp, tb, te, rb, re);
   float* wcoef = sm.wbuf + warp * S::MAXT;
+  float* wscale = sm.wsc + warp * S::MAXT;
+  float* wys = sm.wy + warp * STAGES * S::DY;
 
-  for (int t = tid; t < S::T; t += NW * 32) sm.smy[t] = static_cast<uint8_t>(__ldg(a.my + t));
+  for (int t = tid; t < S::T; t += NW * 32) sm.smy[t] = static_cast<uint8_t>(__ldg(a.my_k + t));
+  for (int t = tb + lane; t < te; t += 32) wscale[t - tb] = __ldg(a.scale_k + t);
   if (tid == 0) {
     mbar_init(&bars[0], 1);
     mbar_init(&bars[1], 1);
@@ -199,14 +209,20 @@ __global__ void __launch_bounds__(NW * 32) tp_segsum_spec_kernel(FusedArgs a) {
   for (int64_t b = 0; b < nb; ++b) {
     if (b + 1 < nb) issue(b + 1);
     const int set = b & 1;
-    if (!mbar_wait(&bars[set], (b >> 1) & 1)) { failed = true; break; }
     const int64_t eb = e0 + b * STAGES;
     const int cnt = (int)min((int64_t)STAGES, e1 - eb);
+    // the warp's own copy of the batch's harmonics (requested before waiting for the feature rows)
+    for (int q = lane; q < cnt * S::DY; q += 32) {
+      const int64_t e = eb + q / S::DY;
+      wys[q] = __ldg(a.y + (a.yidx ? __ldg(a.yidx + e) : e) * S::DY + q % S::DY);
+    }
+    if (!mbar_wait(&bars[set], (b >> 1) & 1)) { failed = true; break; }
+    __syncwarp();
     for (int s = 0; s < cnt; ++s) {
       const int64_t e = eb + s;
       while (e >= boundary) flush();
-      const float* ye = a.y + (a.yidx ? __ldg(a.yidx + e) : e) * S::DY;
-      for (int t = tb + lane; t < te; t += 32) wcoef[t - tb] = __ldg(a.scale + t) * __ldg(ye + sm.smy[t]);
+      const float* ye = wys + s * S::DY;
+      for (int t = tb + lane; t < te; t += 32) wcoef[t - tb] = wscale[t - tb] * ye[sm.smy[t]];
       __syncwarp();
       float x[S::DF][CPL];
       const float* xr = sm.xs + (set * STAGES + s) * ROWF + lane * CPL;
@@ -238,9 +254,37 @@ __global__ void __launch_bounds__(NW * 32) tp_segsum_spec_kernel(FusedArgs a) {
   while (d_cur < d1) flush();
 }
 
+// Sum each of the N per-lane values over the 32 lanes and store the N totals.  For N = 16 the
+// butterfly halves the number of live values at every step (8 + 4 + 2 + 1 + 1 shuffles instead of 80).
+template <int N>
+__device__ __forceinline__ void warp_reduce_to_smem(float (&v)[N], float* dst, int lane) {
+  if constexpr (N == 16) {
+    float a8[8], a4[4], a2[2];
+    const bool h16 = lane & 16, h8 = lane & 8, h4 = lane & 4, h2 = lane & 2;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a8[i] = (h16 ? v[i + 8] : v[i]) + __shfl_xor_sync(0xffffffffu, h16 ? v[i] : v[i + 8], 16);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) a4[i] = (h8 ? a8[i + 4] : a8[i]) + __shfl_xor_sync(0xffffffffu, h8 ? a8[i] : a8[i + 4], 8);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) a2[i] = (h4 ? a4[i + 2] : a4[i]) + __shfl_xor_sync(0xffffffffu, h4 ? a4[i] : a4[i + 2], 4);
+    float r = (h2 ? a2[1] : a2[0]) + __shfl_xor_sync(0xffffffffu, h2 ? a2[0] : a2[1], 2);
+    r += __shfl_xor_sync(0xffffffffu, r, 1);
+    // lane bits (16, 8, 4, 2) select which of the 16 values this lane ended up with
+    if ((lane & 1) == 0) dst[(h16 ? 8 : 0) + (h8 ? 4 : 0) + (h4 ? 2 : 0) + (h2 ? 1 : 0)] = r;
+  } else {
+#pragma unroll
+    for (int k = 0; k < N; ++k) {
+      float t = v[k];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+      if (lane == 0) dst[k] = t;
+    }
+  }
+}
+
 // ---- spec kernel: adjoint w.r.t. the channel-less operand ----------------------------------------
 template <class S, int CPL>
-__global__ void __launch_bounds__(NW * 32) tp_inner_spec_kernel(FusedArgs a) {
+__global__ void __launch_bounds__(NW * 32, 4) tp_inner_spec_kernel(FusedArgs a) {
   constexpr int C = 32 * CPL, ROWF = S::DF * C;
   constexpr uint32_t ROWB = ROWF * sizeof(float);
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -250,7 +294,7 @@ __global__ void __launch_bounds__(NW * 32) tp_inner_spec_kernel(FusedArgs a) {
   int tb, te, rb, re;
   warp_ranges<S>(warp, tb, te, rb, re);
   float* wscale = sm.wbuf + warp * S::MAXT;
-  for (int t = tb + lane; t < te; t += 32) wscale[t - tb] = __ldg(a.scale + t);
+  for (int t = tb + lane; t < te; t += 32) wscale[t - tb] = __ldg(a.scale_k + t);
   if (tid == 0) {
     mbar_init(&bars[0], 1);
     mbar_init(&bars[1], 1);
@@ -330,13 +374,7 @@ __global__ void __launch_bounds__(NW * 32) tp_inner_spec_kernel(FusedArgs a) {
       else if (warp == 2) S::template inner_w2<CPL>(ay, x, g, sc);
       else S::template inner_w3<CPL>(ay, x, g, sc);
       float* rd = sm.red + ((set * STAGES + s) * NW + warp) * S::DY;
-#pragma unroll
-      for (int k = 0; k < S::DY; ++k) {
-        float v = ay[k];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (lane == 0) rd[k] = v;
-      }
+      warp_reduce_to_smem<S::DY>(ay, rd, lane);
     }
     cta_sync();
     // combine the four warps' partial sums of this batch; the other set is free until the next sync
@@ -431,7 +469,7 @@ bool try_spec(uint64_t key, bool inner, const FusedArgs& a, cudaStream_t s, int&
 
 int run(bool inner, const eqt_tp_table* tab, FusedArgs a, cudaStream_t s) {
   if (a.n_out == 0 || (inner && a.n_edges == 0)) return EQT_OK;
-  if ((reinterpret_cast<uintptr_t>(a.feat) & 15u) == 0 && a.status && (!inner || a.ptr)) {
+  if ((reinterpret_cast<uintptr_t>(a.feat) & 15u) == 0 && a.status && a.scale_k && a.my_k && (!inner || a.ptr)) {
     // nodes per CTA: keep every SM busy with several CTAs but amortise the pipeline prologue
     int64_t per = std::max<int64_t>(1, a.n_out / (148 * 16));
     const int64_t avg_deg = std::max<int64_t>(1, a.n_edges / std::max<int64_t>(1, a.n_out));
@@ -458,6 +496,7 @@ int fill(const eqt_tp_table* tab, FusedArgs& a) {
   if (tab->num_entries < 0 || tab->num_rows < 0 || tab->d_feat <= 0 || tab->d_y <= 0 || tab->d_y > 255)
     return fail(EQT_ERR_BAD_ARGUMENT, "bad table sizes");
   a.scale = tab->scale; a.mf = tab->m_feat; a.my = tab->m_y; a.rowptr = tab->row_ptr;
+  a.scale_k = tab->scale_k; a.my_k = tab->m_y_k;
   a.T = tab->num_entries; a.R = tab->num_rows; a.DF = tab->d_feat; a.DY = tab->d_y;
   return EQT_OK;
 }
