@@ -12,8 +12,7 @@ from torch import Tensor
 from .. import _lib
 
 
-def gather_rows(x: Tensor, index: Tensor) -> Tensor:
-    """``out[e] = x[index[e]]`` for a contiguous ``x`` of shape (rows, ...)."""
+def _gather_rows_raw(x: Tensor, index: Tensor) -> Tensor:
     dev = _lib.require_cuda(x, index)
     x = x.contiguous()
     width = x[0].numel() if x.shape[0] else 0
@@ -25,8 +24,7 @@ def gather_rows(x: Tensor, index: Tensor) -> Tensor:
     return out
 
 
-def segment_sum(x: Tensor, ptr: Tensor, perm: Optional[Tensor] = None) -> Tensor:
-    """``out[d] = sum_{e in [ptr[d], ptr[d+1])} x[perm[e] or e]`` (ascending e, deterministic)."""
+def _segment_sum_raw(x: Tensor, ptr: Tensor, perm: Optional[Tensor] = None) -> Tensor:
     dev = _lib.require_cuda(x, ptr, perm)
     x = x.contiguous()
     width = x[0].numel() if x.shape[0] else int(torch.tensor(x.shape[1:]).prod())
@@ -36,3 +34,50 @@ def segment_sum(x: Tensor, ptr: Tensor, perm: Optional[Tensor] = None) -> Tensor
                                               None if perm is None else perm.contiguous().data_ptr(), out.data_ptr(),
                                               ptr.shape[0] - 1, width, _lib.stream_ptr(dev)), "eqt_segment_sum")
     return out
+
+
+class _GatherRows(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, index):
+        ctx.save_for_backward(index)
+        ctx.rows = x.shape[0]
+        return _gather_rows_raw(x, index)
+
+    @staticmethod
+    def backward(ctx, grad):
+        (index,) = ctx.saved_tensors
+        out = torch.zeros(ctx.rows, *grad.shape[1:], dtype=grad.dtype, device=grad.device)
+        return out.index_add_(0, index, grad), None
+
+
+class _SegmentSum(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, ptr, perm):
+        ctx.save_for_backward(ptr, perm)
+        ctx.rows = x.shape[0]
+        return _segment_sum_raw(x, ptr, perm)
+
+    @staticmethod
+    def backward(ctx, grad):
+        ptr, perm = ctx.saved_tensors
+        node = torch.repeat_interleave(torch.arange(ptr.numel() - 1, device=ptr.device), ptr[1:] - ptr[:-1])
+        g = _gather_rows_raw(grad.contiguous(), node)            # gradient of the e-th summed row
+        if perm is None:
+            if g.shape[0] == ctx.rows:
+                return g, None, None
+            out = torch.zeros(ctx.rows, *g.shape[1:], dtype=g.dtype, device=g.device)
+            out[int(ptr[0]):int(ptr[0]) + g.shape[0]] = g
+            return out, None, None
+        out = torch.zeros(ctx.rows, *g.shape[1:], dtype=g.dtype, device=g.device)
+        return out.index_add_(0, perm, g), None, None
+
+
+def gather_rows(x: Tensor, index: Tensor) -> Tensor:
+    """``out[e] = x[index[e]]`` for ``x`` of shape (rows, ...); differentiable in ``x``."""
+    return _GatherRows.apply(x, index)
+
+
+def segment_sum(x: Tensor, ptr: Tensor, perm: Optional[Tensor] = None) -> Tensor:
+    """``out[d] = sum_{e in [ptr[d], ptr[d+1])} x[perm[e] or e]`` (ascending e, no atomics, deterministic);
+    differentiable in ``x``."""
+    return _SegmentSum.apply(x, ptr, perm)
