@@ -30,6 +30,7 @@
 
 #include <algorithm>
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 
@@ -41,16 +42,27 @@ constexpr int KB = 32;                 // floats per k-block = one 128-byte swiz
 constexpr int TILE_M = 128;
 constexpr int TC_WAIT_SPINS = 1 << 21;
 
-struct MixArgs {
-  float* out;          // first output element of (node 0, m 0)
-  int64_t out_node_stride, out_m_stride;   // in floats; a row holds `cout` contiguous floats
-  int64_t n;           // nodes
-  int dim;             // components of the output irrep
-  int npt;             // nodes per tile (npt * dim <= 128)
-  int kblocks;         // K / 32
-  int cout;            // N
+constexpr int MAX_JOBS = 8;
+
+struct alignas(64) JobDev {
+  CUtensorMap map_a, map_bb, map_bs;        // A (3-D: k, m, node), B big / small (2-D: k, column)
+  float* out;                               // first output element of (node 0, m 0)
+  int64_t out_node_stride, out_m_stride;    // in floats; a row holds n_cols contiguous floats
+  int64_t tile_begin;                       // position of the job's first tile in the launch's work list
+  int dim;                                  // rows per node
+  int npt;                                  // nodes per tile (npt * dim <= 128)
+  int kblocks;                              // K / 32
+  int n_cols;                               // N of this job
+};
+
+struct MixLaunch {
+  JobDev job[MAX_JOBS];
+  int64_t n;            // nodes
+  int64_t total_tiles;
+  int num_jobs;
+  int max_cols;         // largest N among the jobs: fixes the stage layout and the TMEM split
   int stages;
-  int tmem_cols;       // power of two >= 2 * cout
+  int tmem_cols;        // power of two >= 2 * max_cols
   int* status;
 };
 
@@ -210,42 +222,52 @@ struct GemmJob {
   int64_t out_node_stride, out_m_stride;   // floats
 };
 
-int launch_job(const GemmJob& j, int64_t n, int* status, cudaStream_t st) {
-  const uint32_t a_bytes = TILE_M * KB * 4, b_bytes = (uint32_t)j.N * KB * 4;
-  const uint32_t stage_bytes = 2 * a_bytes + 2 * b_bytes;
-  const int stages = (int)std::min<size_t>(8, (220 * 1024 - 1024) / stage_bytes);
-  if (stages < 2) return fail(EQT_ERR_UNSUPPORTED, "tile too wide for the shared-memory ring");
-  const size_t smem = (size_t)stages * stage_bytes + 1024;
+int launch_jobs(const GemmJob* jobs, int count, int64_t n, int* status, cudaStream_t st) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(mix_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     if (e != cudaSuccess) return fail(EQT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     configured = true;
   }
-  MixArgs a{};
-  a.out = j.out; a.out_node_stride = j.out_node_stride; a.out_m_stride = j.out_m_stride;
-  a.n = n; a.dim = j.dim; a.npt = TILE_M / j.dim; a.kblocks = (int)(j.K / KB); a.cout = j.N;
-  a.stages = stages; a.status = status;
-  a.tmem_cols = 32;
-  while (a.tmem_cols < 2 * j.N) a.tmem_cols <<= 1;
-  CUtensorMap map_a, map_bb, map_bs;
-  {
-    cuuint64_t dims[3] = {(cuuint64_t)j.K, (cuuint64_t)j.dim, (cuuint64_t)n};
-    cuuint64_t strides[2] = {(cuuint64_t)j.a_m_stride * 4, (cuuint64_t)j.a_node_stride * 4};
-    cuuint32_t box[3] = {KB, (cuuint32_t)j.dim, (cuuint32_t)a.npt};
-    if (int rc = make_map(&map_a, j.a, 3, dims, strides, box)) return rc;
+  for (int first = 0; first < count; first += MAX_JOBS) {
+    const int m = std::min(MAX_JOBS, count - first);
+    MixLaunch L{};
+    L.n = n; L.num_jobs = m; L.status = status;
+    for (int q = 0; q < m; ++q) L.max_cols = std::max(L.max_cols, jobs[first + q].N);
+    const uint32_t a_bytes = TILE_M * KB * 4, b_bytes = (uint32_t)L.max_cols * KB * 4;
+    const uint32_t stage_bytes = 2 * a_bytes + 2 * b_bytes;
+    L.stages = (int)std::min<size_t>(8, (220 * 1024 - 1024) / stage_bytes);
+    if (L.stages < 2) return fail(EQT_ERR_UNSUPPORTED, "tile too wide for the shared-memory ring");
+    L.tmem_cols = 32;
+    while (L.tmem_cols < 2 * L.max_cols) L.tmem_cols <<= 1;
+    int64_t total = 0;
+    for (int q = 0; q < m; ++q) {
+      const GemmJob& j = jobs[first + q];
+      JobDev& d = L.job[q];
+      d.out = j.out; d.out_node_stride = j.out_node_stride; d.out_m_stride = j.out_m_stride;
+      d.dim = j.dim; d.npt = TILE_M / j.dim; d.kblocks = (int)(j.K / KB); d.n_cols = j.N;
+      d.tile_begin = total;
+      total += ceil_div(n, d.npt);
+      {
+        cuuint64_t dims[3] = {(cuuint64_t)j.K, (cuuint64_t)j.dim, (cuuint64_t)n};
+        cuuint64_t strides[2] = {(cuuint64_t)j.a_m_stride * 4, (cuuint64_t)j.a_node_stride * 4};
+        cuuint32_t box[3] = {KB, (cuuint32_t)j.dim, (cuuint32_t)d.npt};
+        if (int rc = make_map(&d.map_a, j.a, 3, dims, strides, box)) return rc;
+      }
+      {
+        cuuint64_t dims[2] = {(cuuint64_t)j.K, (cuuint64_t)j.N};
+        cuuint64_t strides[1] = {(cuuint64_t)j.K * 4};
+        cuuint32_t box[2] = {KB, (cuuint32_t)j.N};
+        if (int rc = make_map(&d.map_bb, j.b_big, 2, dims, strides, box)) return rc;
+        if (int rc = make_map(&d.map_bs, j.b_small, 2, dims, strides, box)) return rc;
+      }
+    }
+    L.total_tiles = total;
+    const unsigned grid = (unsigned)std::min<int64_t>(total, sm_count());
+    mix_tc_kernel<<<grid, TC_THREADS, (size_t)L.stages * stage_bytes + 1024, st>>>(L);
+    if (int rc = check_launch("mix_tc_kernel")) return rc;
   }
-  {
-    cuuint64_t dims[2] = {(cuuint64_t)j.K, (cuuint64_t)j.N};
-    cuuint64_t strides[1] = {(cuuint64_t)j.K * 4};
-    cuuint32_t box[2] = {KB, (cuuint32_t)j.N};
-    if (int rc = make_map(&map_bb, j.b_big, 2, dims, strides, box)) return rc;
-    if (int rc = make_map(&map_bs, j.b_small, 2, dims, strides, box)) return rc;
-  }
-  const int64_t tiles = ceil_div(n, a.npt);
-  const unsigned grid = (unsigned)std::min<int64_t>(tiles, sm_count());
-  mix_tc_kernel<<<grid, TC_THREADS, smem, st>>>(map_a, map_bb, map_bs, a);
-  return check_launch("mix_tc_kernel");
+  return EQT_OK;
 }
 
 int check_common(const void* a, const void* b, const void* c, const void* d, const eqt_mix_block* blocks, int32_t* status,
@@ -271,6 +293,7 @@ extern "C" int eqt_mix_tc(const float* s, const float* w_big, const float* w_sma
     return rc < 0 ? EQT_OK : rc;
   if (cin % KB != 0 || cout % 16 != 0 || cout > 256)
     return fail(EQT_ERR_UNSUPPORTED, "tensor-core mix needs C_in %% 32 == 0 and C_out %% 16 == 0, C_out <= 256");
+  std::vector<GemmJob> jobs;
   for (int b = 0; b < num_blocks; ++b) {
     const eqt_mix_block& blk = blocks[b];
     if (blk.dim <= 0 || blk.dim > TILE_M || blk.paths <= 0) return fail(EQT_ERR_BAD_ARGUMENT, "bad block %d", b);
@@ -279,9 +302,9 @@ extern "C" int eqt_mix_tc(const float* s, const float* w_big, const float* w_sma
     j.a = s + (int64_t)blk.in_row0 * cin; j.a_m_stride = j.K; j.a_node_stride = (int64_t)rows * cin;
     j.b_big = w_big + blk.w_offset; j.b_small = w_small + blk.w_offset; j.N = cout;
     j.out = out + (int64_t)blk.out_row0 * cout; j.out_node_stride = (int64_t)comps * cout; j.out_m_stride = cout;
-    if (int rc = launch_job(j, n, status, static_cast<cudaStream_t>(stream))) return rc;
+    jobs.push_back(j);
   }
-  return EQT_OK;
+  return launch_jobs(jobs.data(), (int)jobs.size(), n, status, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int eqt_mix_tc_transposed(const float* g, const float* w_big, const float* w_small, float* g_inter,
@@ -292,6 +315,7 @@ extern "C" int eqt_mix_tc_transposed(const float* g, const float* w_big, const f
     return rc < 0 ? EQT_OK : rc;
   if (cout % KB != 0 || cin % 16 != 0)
     return fail(EQT_ERR_UNSUPPORTED, "transposed tensor-core mix needs C_out %% 32 == 0 and C_in %% 16 == 0");
+  std::vector<GemmJob> jobs;
   for (int b = 0; b < num_blocks; ++b) {
     const eqt_mix_block& blk = blocks[b];
     if (blk.dim <= 0 || blk.dim > TILE_M || blk.paths <= 0) return fail(EQT_ERR_BAD_ARGUMENT, "bad block %d", b);
@@ -305,10 +329,10 @@ extern "C" int eqt_mix_tc_transposed(const float* g, const float* w_big, const f
       j.b_big = w_big + blk.w_offset + c0 * cout; j.b_small = w_small + blk.w_offset + c0 * cout;
       j.N = (int)std::min<int64_t>(chunk_max, width - c0);
       j.out = g_inter + (int64_t)blk.in_row0 * cin + c0; j.out_node_stride = (int64_t)rows * cin; j.out_m_stride = width;
-      if (int rc = launch_job(j, n, status, static_cast<cudaStream_t>(stream))) return rc;
+      jobs.push_back(j);
     }
   }
-  return EQT_OK;
+  return launch_jobs(jobs.data(), (int)jobs.size(), n, status, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int eqt_wgrad_tc(const float* s, const float* g, float* gw_packed, float* scratch, int64_t scratch_floats,
@@ -433,4 +457,66 @@ extern "C" int eqt_wgrad_tc_static(const float* s, const float* g, float* gw_pac
   if (int rc = static_scratch(&scratch)) return rc;
   return eqt_wgrad_tc(s, g, gw_packed, scratch, kStaticScratchFloats, n, rows, comps, cin, cout, blocks, num_blocks,
                       status, stream);
+}
+
+// ------------------------------------------------------------------------------------------
+// Packing and splitting of the weights for the GEMMs above (one launch instead of a dozen tensor ops)
+// ------------------------------------------------------------------------------------------
+namespace eqt {
+namespace {
+
+struct PackArgs {
+  int first[16], paths[16];      // per block: first gathered path, number of paths
+  int num_blocks, cin, cout, k_major;
+  int64_t total;
+};
+
+// k_major = 1: per block Bt[co, p*cin + ci] (operand of eqt_mix_tc);  0: [p*cin + ci, co] (stacked paths)
+__global__ void __launch_bounds__(256) pack_weights_kernel(const float* __restrict__ w, const int64_t* __restrict__ gather,
+                                                           float* __restrict__ big, float* __restrict__ small, PackArgs a) {
+  const int64_t per_path = (int64_t)a.cin * a.cout;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < a.total; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t g = i / per_path;              // gathered path this element belongs to (blocks are contiguous runs)
+    const int64_t r = i % per_path;
+    int ci, co;
+    if (a.k_major) {
+      int b = 0;
+      while (b + 1 < a.num_blocks && g >= a.first[b + 1]) ++b;
+      const int64_t local = i - (int64_t)a.first[b] * per_path;      // offset inside the block's (cout, paths*cin) matrix
+      const int64_t kk = local % ((int64_t)a.paths[b] * a.cin);
+      co = (int)(local / ((int64_t)a.paths[b] * a.cin));
+      g = a.first[b] + kk / a.cin;
+      ci = (int)(kk % a.cin);
+    } else {
+      ci = (int)(r / a.cout);
+      co = (int)(r % a.cout);
+    }
+    const float v = __ldg(w + __ldg(gather + g) * per_path + (int64_t)ci * a.cout + co);
+    const float hi = rn_tf32(v);
+    big[i] = hi;
+    small[i] = rn_tf32(v - hi);
+  }
+}
+
+}  // namespace
+}  // namespace eqt
+
+extern "C" int eqt_pack_weights(const float* w, const int64_t* path_gather, int32_t cin, int32_t cout,
+                                const eqt_mix_block* blocks, int32_t num_blocks, int32_t k_major, float* big,
+                                float* small, void* stream) {
+  using namespace eqt;
+  if (!w || !path_gather || !blocks || !big || !small) return fail(EQT_ERR_BAD_ARGUMENT, "NULL pointer");
+  if (num_blocks <= 0 || num_blocks > 16 || cin <= 0 || cout <= 0) return fail(EQT_ERR_UNSUPPORTED, "1..16 blocks supported");
+  PackArgs a{};
+  a.num_blocks = num_blocks; a.cin = cin; a.cout = cout; a.k_major = k_major;
+  int total_paths = 0;
+  for (int b = 0; b < num_blocks; ++b) {
+    a.first[b] = (int)(blocks[b].w_offset / ((int64_t)cin * cout));
+    a.paths[b] = blocks[b].paths;
+    if (a.first[b] != total_paths) return fail(EQT_ERR_BAD_ARGUMENT, "blocks must be packed back to back");
+    total_paths += blocks[b].paths;
+  }
+  a.total = (int64_t)total_paths * cin * cout;
+  pack_weights_kernel<<<flat_grid(a.total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(w, path_gather, big, small, a);
+  return check_launch("pack_weights_kernel");
 }

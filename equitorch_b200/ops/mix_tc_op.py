@@ -59,15 +59,20 @@ class MixPlan:
             self._struct_cache[key] = arr
         return self._struct_cache[key]
 
-    def pack(self, weight: Tensor):
-        """(P, cin, cout) -> per block (cout, paths*cin) row-major, concatenated; split into big + small."""
-        g = weight.detach().index_select(0, self.path_gather)      # (sum paths, cin, cout)
-        parts = []
-        for in0, out0, dim, paths, first in self.blocks_host:
-            parts.append(g[first:first + paths].permute(2, 0, 1).reshape(-1))
-        packed = torch.cat(parts).contiguous()
-        big = _round_tf32(packed)
-        return big, _round_tf32(packed - big)
+    def pack(self, weight: Tensor, k_major: bool = True):
+        """Gather the blocks' paths from ``weight`` (P, cin, cout), lay them out for the GEMM (per block
+        (cout, paths*cin) when ``k_major`` else stacked (paths*cin, cout)) and split into big + small."""
+        w = weight.detach().contiguous()
+        cin, cout = w.shape[-2:]
+        n = self.path_gather.numel() * cin * cout
+        big = torch.empty(n, dtype=torch.float32, device=w.device)
+        small = torch.empty(n, dtype=torch.float32, device=w.device)
+        blocks = self.structs(cin, cout)
+        with torch.cuda.device(w.device):
+            _lib.check(_lib.lib().eqt_pack_weights(w.data_ptr(), self.path_gather.data_ptr(), cin, cout, blocks,
+                                                   len(blocks), int(k_major), big.data_ptr(), small.data_ptr(),
+                                                   _lib.stream_ptr(w.device)), "eqt_pack_weights")
+        return big, small
 
 
 def mix_tc_transposed(g: Tensor, weight: Tensor, plan: MixPlan) -> Tensor:
@@ -78,9 +83,7 @@ def mix_tc_transposed(g: Tensor, weight: Tensor, plan: MixPlan) -> Tensor:
     n, comps, cout = g.shape
     cin = weight.shape[-2]
     assert comps == plan.comps and weight.shape[-1] == cout
-    stacked = weight.detach().index_select(0, plan.path_gather).reshape(-1)     # blocks are contiguous runs of paths
-    big = _round_tf32(stacked)
-    small = _round_tf32(stacked - big)
+    big, small = plan.pack(weight, k_major=False)
     out = torch.empty(n, plan.rows, cin, dtype=torch.float32, device=dev)
     blocks = plan.structs(cin, cout)
     with torch.cuda.device(dev):
@@ -131,11 +134,6 @@ def supported_wgrad(cin: int, cout: int) -> bool:
 
 def supported_transposed(cin: int, cout: int) -> bool:
     return cout % 32 == 0 and cin % 16 == 0 and cin <= 256
-
-
-def _round_tf32(x: Tensor) -> Tensor:
-    """Round to the nearest value with 10 mantissa bits (ties away from zero, like ``cvt.rna.tf32.f32``)."""
-    return ((x.view(torch.int32) + 0x1000) & -8192).view(torch.float32)
 
 
 def supported(cin: int, cout: int) -> bool:

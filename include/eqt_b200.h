@@ -254,6 +254,16 @@ int eqt_wgrad_tc_static(const float* s, const float* g, float* gw_packed, int64_
                         int32_t* status, void* stream);
 int64_t eqt_wgrad_tc_static_capacity(void);
 
+/*
+ * Gather, lay out and split shared weights w (num_paths, cin, cout) for the tensor-core entry points:
+ * path_gather (device, int64) lists the paths of all blocks back to back (w_offset of a block =
+ * first gathered path * cin * cout).  k_major != 0 writes the per-block (cout, paths*cin) matrices that
+ * eqt_mix_tc reads, k_major == 0 the stacked (paths*cin, cout) matrices of eqt_mix_tc_transposed;
+ * big = TF32-rounded value, small = TF32-rounded remainder.  No counterpart in the reference.
+ */
+int eqt_pack_weights(const float* w, const int64_t* path_gather, int32_t cin, int32_t cout, const eqt_mix_block* blocks,
+                     int32_t num_blocks, int32_t k_major, float* big, float* small, void* stream);
+
 /* Library / device facts. */
 const char* eqt_last_error(void);
 int eqt_version(void);
