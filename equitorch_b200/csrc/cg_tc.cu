@@ -18,7 +18,7 @@
 //  * B operand (features): TMA boxes of (32 channels, D components, 1 node) gathered by edge source
 //    into the MN-major "128B swizzle, 32-byte atom" layout.
 //  * float32 accuracy by the 3xTF32 split of both operands (big*big + big*small + small*big).
-//  * Roles: warp 0 TMA producer, warp 1 MMA issue + TMEM, warps 2-9 builders (coefficients, split of
+//  * Roles: warp 0 producer (indices, harmonics by cp.async, features by TMA), warp 1 MMA issue + TMEM, warps 2-9 builders (coefficients, split of
 //    the features), warps 10-13 epilogue (one accumulator per node, double buffered, rows < R stored).
 //  * All waits are bounded; on expiry the status flag is raised and the kernel winds down.
 //
@@ -57,6 +57,14 @@ struct CgArgs {
   int* status;
 };
 
+__device__ __forceinline__ void cp_async_4(void* dst_smem, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(s32(dst_smem)), "l"(src) : "memory");
+}
+// the barrier gets one arrival (already counted in its init count) once this thread's earlier cp.async have landed
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(s32(bar)) : "memory");
+}
+
 // byte offset of element (row r, k) inside a K-major 128B-swizzled tile of 128-byte rows
 __device__ __forceinline__ uint32_t a_tile_offset(int r, int k) {
   return (uint32_t)(r * 128 + ((((k >> 2) ^ (r & 7)) & 7) << 4) + ((k & 3) << 2));
@@ -68,6 +76,8 @@ cg_segsum_tc_kernel(const __grid_constant__ CUtensorMap map_x, CgArgs p) {
   __shared__ uint64_t bar_full[8], bar_ready[8], bar_empty[8], bar_acc_full[2], bar_acc_empty[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+  __shared__ __align__(16) float ys[8][EPB * KE];   // harmonics rows of the k-block in each stage
+  __shared__ int4 kb_meta[8];                        // {edges in the k-block, first of its node, last of its node, stop}
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int atoms = p.C / 32;
@@ -82,7 +92,7 @@ cg_segsum_tc_kernel(const __grid_constant__ CUtensorMap map_x, CgArgs p) {
   if (tid == 0) {
     abort_flag = 0;
     for (int s = 0; s < p.stages; ++s) {
-      bar_init(&bar_full[s], 1);
+      bar_init(&bar_full[s], 1 + 32);           // lane 0's expect_tx + one cp.async arrival per producer lane
       bar_init(&bar_ready[s], CG_BUILDER_WARPS);
       bar_init(&bar_empty[s], 1);
     }

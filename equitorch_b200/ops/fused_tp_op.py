@@ -63,7 +63,7 @@ class TpTable:
         Returns ``None`` when the structure does not fit that kernel (more than two harmonics terms per
         coefficient, more than 128 rows, 16 feature components or 512 coefficients).
         """
-        if s.num_rows > 128 or s.d_feat > 16 or s.d_y > 256 or len(s.mf) == 0:
+        if s.num_rows > 128 or s.d_feat > 16 or s.d_y > 16 or len(s.mf) == 0:
             return None
         slot = s.row * s.d_feat + s.mf
         uniq, inv, counts = np.unique(slot, return_inverse=True, return_counts=True)
@@ -92,8 +92,10 @@ def _f32(t: Tensor, what: str) -> Tensor:
     return t.contiguous()
 
 
-#: route ``cg_segment_sum`` through the tcgen05 kernel when the table and the shapes allow it
-TENSOR_CORE_CG = True
+#: route ``cg_segment_sum`` through the tcgen05 kernel when the table and the shapes allow it.  Off by
+#: default: at l_max = 3, C = 64 the dense per-edge coefficient matrix costs 17x the flops of the sparse
+#: loop and the kernel measured 8.2 ms against 4.0 ms for the CUDA-core kernel (2M edges, B200).
+TENSOR_CORE_CG = False
 
 
 def tensor_core_cg_supported(table: TpTable, feat: Tensor, seg_ptr: Optional[Tensor], n_edges: int) -> bool:
