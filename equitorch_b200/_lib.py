@@ -45,7 +45,7 @@ class ShTable(C.Structure):
 class TpTableStruct(C.Structure):
     _fields_ = [("scale", C.c_void_p), ("m_feat", C.c_void_p), ("m_y", C.c_void_p), ("row_ptr", C.c_void_p),
                 ("num_entries", C.c_int32), ("num_rows", C.c_int32), ("d_feat", C.c_int32), ("d_y", C.c_int32),
-                ("structure_key", C.c_uint64), ("scale_k", C.c_void_p), ("m_y_k", C.c_void_p)]
+                ("structure_key", C.c_uint64), ("scale_o", C.c_void_p)]
 
 
 class CgTcTableStruct(C.Structure):

@@ -1,12 +1,11 @@
 """Generate ``generated/tp_specs.inc``: fully unrolled Clebsch-Gordan inner loops.
 
-The fused tensor-product kernels keep the gathered feature rows, the per-edge CG
-coefficients and the accumulators in registers.  Registers cannot be indexed at run time,
-so for the index structures that matter (the registry below) the loop over the table
-entries is emitted as straight-line code, one function per warp of the CTA: each warp
-owns a contiguous range of intermediate rows (and hence of table entries), balanced by
-entry count.  Only the *index structure* is baked in; the CG values stay run-time data
-(``scale``), so path / channel normalisation do not need their own code.
+The fused tensor-product kernels keep the gathered feature row, the per-node outer-product
+accumulators and the CG sums in registers.  Registers cannot be indexed at run time, so for
+the index structures that matter (the registry below) the loops over the accumulator cells
+and over the table entries are emitted as straight-line code, one set of functions per warp
+role (see ``OuterPlan``).  Only the *index structure* is baked in; the CG values stay
+run-time data (``scale``), so path / channel normalisation do not need their own code.
 
 A structure is identified by ``structure_key`` (a hash of T, R, D_feat, D_y and the three
 index columns); ``equitorch_b200.fused`` computes the same key from a layer's tables and
@@ -24,7 +23,6 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "generated", "tp_specs.inc")
-NUM_WARPS = 4
 
 # (irreps_out, irreps_in1, irreps_in2) of layers whose inner loops are unrolled at build time.
 # All role rotations (forward, gradient w.r.t. input1, gradient w.r.t. input2) are generated.
@@ -64,86 +62,150 @@ def structure_from_info(info, feat_is_input1: bool, d_feat: int, d_y: int) -> St
     return Structure(mf.astype(np.int64), my.astype(np.int64), row.astype(np.int64), d_feat, d_y, info.out_size)
 
 
-def partition(s: Structure, warps: int = NUM_WARPS):
-    """Split the rows into ``warps`` contiguous groups with balanced entry counts."""
-    t = len(s.row)
-    starts = np.searchsorted(s.row, np.arange(s.num_rows + 1))      # first entry of each row
-    wr = [0]
-    for w in range(1, warps):
-        target = t * w / warps
-        r = int(np.argmin(np.abs(starts - target)))
-        wr.append(max(r, wr[-1]))
-    wr.append(s.num_rows)
-    wt = [int(starts[r]) for r in wr]
-    return wt, wr
+NUM_ROLES = 2
 
 
-def kernel_order(s: Structure, warps: int = NUM_WARPS) -> np.ndarray:
-    """Order in which the unrolled code visits the table entries (a permutation of ``range(T)``).
+class OuterPlan(NamedTuple):
+    """Split of a structure for the outer-product kernels.
 
-    Inside a warp's range the entries are interleaved across rows (first entry of every row, then
-    the second of every row, ...), so that consecutive FMAs hit different accumulators instead of
-    forming one dependent chain per row.  The run-time arrays handed to the unrolled kernels
-    (``scale``, ``m_y``) are stored in this order.
+    The sum over the edges of a node commutes with the CG contraction:
+    ``S[d, r] = sum_t scale[t] * Q_d[m_y[t], m_feat[t]]`` with ``Q_d = sum_e y_e (x) x_e``.  A *cell* is a
+    pair (m_y, m_feat) that some entry uses.  Cells that share a row are tied together; the resulting
+    groups (for irreps tables: the (l_y, l_feat) blocks) are dealt to ``NUM_ROLES`` warps so that every
+    row is produced by exactly one warp from accumulators it holds itself.
     """
-    wt, _ = partition(s, warps)
-    order = []
-    for w in range(warps):
-        ts = np.arange(wt[w], wt[w + 1])
-        if len(ts) == 0:
+    cells: List[np.ndarray]      # per role: (n, 2) array of (m_y, m_feat), its accumulator order
+    rows: List[np.ndarray]       # per role: rows it produces, ascending
+    entries: List[np.ndarray]    # per role: entry ids sorted by row
+    offsets: List[int]           # start of each role's block in the permuted scale array (multiples of 4)
+
+
+def outer_plan(s: Structure, roles: int = NUM_ROLES) -> OuterPlan:
+    cell_id = s.my * s.d_feat + s.mf
+    parent = {int(c): int(c) for c in np.unique(cell_id)}
+
+    def find(c):
+        while parent[c] != c:
+            parent[c] = parent[parent[c]]
+            c = parent[c]
+        return c
+
+    starts = np.searchsorted(s.row, np.arange(s.num_rows + 1))
+    for r in range(s.num_rows):
+        cs = cell_id[starts[r]:starts[r + 1]]
+        for c in cs[1:]:
+            ra, rb = find(int(cs[0])), find(int(c))
+            if ra != rb:
+                parent[max(ra, rb)] = min(ra, rb)
+    groups = {}
+    for c in parent:
+        groups.setdefault(find(c), []).append(c)
+    # largest group first onto the lightest role (ties: lowest role) - deterministic
+    order = sorted(groups.items(), key=lambda kv: (-len(kv[1]), kv[0]))
+    load = [0] * roles
+    owner = {}
+    for root, members in order:
+        w = min(range(roles), key=lambda i: (load[i], i))
+        load[w] += len(members)
+        for c in members:
+            owner[c] = w
+    cells, rows, entries, offsets = [], [], [], [0]
+    for w in range(roles):
+        cw = np.array(sorted(c for c in owner if owner[c] == w), dtype=np.int64)
+        cells.append(np.stack([cw // s.d_feat, cw % s.d_feat], axis=1) if len(cw) else np.zeros((0, 2), np.int64))
+        tw = np.array([t for t in range(len(s.row)) if owner[int(cell_id[t])] == w], dtype=np.int64)
+        entries.append(tw)
+        rw = set(int(r) for r in s.row[tw])
+        if w == 0:                                     # rows without any entry are written (as zeros) by role 0
+            rw |= set(range(s.num_rows)) - set(int(r) for r in s.row)
+        rows.append(np.array(sorted(rw), dtype=np.int64))
+        offsets.append(offsets[-1] + ((len(tw) + 3) // 4) * 4)
+    return OuterPlan(cells, rows, entries, offsets)
+
+
+def outer_order(s: Structure) -> np.ndarray:
+    """Entry ids in the order the outer-product kernels read ``scale`` (-1 = padding to a multiple of 4)."""
+    plan = outer_plan(s)
+    out = np.full(plan.offsets[-1], -1, dtype=np.int64)
+    for w, tw in enumerate(plan.entries):
+        out[plan.offsets[w]:plan.offsets[w] + len(tw)] = tw
+    return out
+
+
+def _emit_outer_role(s: Structure, plan: OuterPlan, w: int) -> List[str]:
+    cells, tw = plan.cells[w], plan.entries[w]
+    index = {(int(k), int(m)): i for i, (k, m) in enumerate(cells)}
+    out = []
+    # per edge: q[cell] += x[m_feat] * y[m_y]
+    out.append(f"  __device__ __forceinline__ static void outer_r{w}(float (&q)[MAXCELL], const float (&x)[DF], const float (&y)[DY]) {{")
+    for i, (k, m) in enumerate(cells):
+        out.append(f"    q[{i}] = fmaf(x[{int(m)}], y[{int(k)}], q[{i}]);")
+    out.append("  }")
+    # per node: rows of this role from the accumulators
+    out.append(f"  template <int CS> __device__ __forceinline__ static void node_r{w}(const float (&q)[MAXCELL], const float4* sc, float* o) {{")
+    out.append("    float4 c; float v;")
+    pos = {int(t): i for i, t in enumerate(tw)}
+    by_row = {}
+    for t in tw:
+        by_row.setdefault(int(s.row[t]), []).append(int(t))
+    loaded = -1
+    for r in plan.rows[w]:
+        ts = by_row.get(int(r), [])
+        if not ts:
+            out.append(f"    o[{int(r)} * CS] = 0.f;")
             continue
-        rows = s.row[ts]
-        pos = ts - np.searchsorted(rows, rows, side="left") - wt[w]      # index of the entry within its row
-        order.append(ts[np.lexsort((rows, pos))])
-    return np.concatenate(order) if order else np.zeros(0, dtype=np.int64)
-
-
-def _emit_segsum(s: Structure, order, wt, wr, w: int) -> List[str]:
-    lines = []
-    tb, te, rb = wt[w], wt[w + 1], wr[w]
-    for q0 in range(tb, te, 4):
-        lines.append(f"    c = cf[{(q0 - tb) // 4}];")
-        for q in range(q0, min(q0 + 4, te)):
-            comp, t = "xyzw"[q - q0], int(order[q])
-            r, m = int(s.row[t]) - rb, int(s.mf[t])
-            lines.append(f"    EQT_FMA_ROW(acc[{r}], c.{comp}, x[{m}]);")
-    return lines
-
-
-def _emit_inner(s: Structure, order, wt, wr, w: int) -> List[str]:
-    lines = []
-    tb, te, rb = wt[w], wt[w + 1], wr[w]
-    for q0 in range(tb, te, 4):
-        lines.append(f"    c = sc[{(q0 - tb) // 4}];")
-        for q in range(q0, min(q0 + 4, te)):
-            comp, t = "xyzw"[q - q0], int(order[q])
-            r, m, k = int(s.row[t]) - rb, int(s.mf[t]), int(s.my[t])
-            lines.append(f"    ay[{k}] = fmaf(c.{comp}, EQT_DOT_ROW(x[{m}], g[{r}]), ay[{k}]);")
-    return lines
+        for n, t in enumerate(ts):
+            i = pos[t]
+            if i // 4 != loaded:
+                loaded = i // 4
+                out.append(f"    c = sc[{loaded}];")
+            term = f"c.{'xyzw'[i % 4]}"
+            cell = index[(int(s.my[t]), int(s.mf[t]))]
+            out.append(f"    v = {term} * q[{cell}];" if n == 0 else f"    v = fmaf({term}, q[{cell}], v);")
+        out.append(f"    o[{int(r)} * CS] = v;")
+    out.append("  }")
+    # adjoint, per node: h[cell] = sum_t scale[t] * g[row[t]]
+    out.append(f"  template <int CS> __device__ __forceinline__ static void hbuild_r{w}(float (&h)[MAXCELL], const float4* sc, const float* g) {{")
+    out.append("    float4 c; float gr;")
+    touched = set()
+    loaded = -1
+    for r in plan.rows[w]:
+        ts = by_row.get(int(r), [])
+        if not ts:
+            continue
+        out.append(f"    gr = g[{int(r)} * CS];")
+        for t in ts:
+            i = pos[t]
+            if i // 4 != loaded:
+                loaded = i // 4
+                out.append(f"    c = sc[{loaded}];")
+            term = f"c.{'xyzw'[i % 4]}"
+            cell = index[(int(s.my[t]), int(s.mf[t]))]
+            if cell in touched:
+                out.append(f"    h[{cell}] = fmaf({term}, gr, h[{cell}]);")
+            else:
+                touched.add(cell)
+                out.append(f"    h[{cell}] = {term} * gr;")
+    out.append("  }")
+    # adjoint, per edge: ay[m_y] += x[m_feat] * h[cell]
+    out.append(f"  __device__ __forceinline__ static void dot_r{w}(float (&ay)[DY], const float (&x)[DF], const float (&h)[MAXCELL]) {{")
+    for i, (k, m) in enumerate(cells):
+        out.append(f"    ay[{int(k)}] = fmaf(x[{int(m)}], h[{i}], ay[{int(k)}]);")
+    out.append("  }")
+    return out
 
 
 def emit_spec(idx: int, s: Structure, note: str) -> str:
-    wt, wr = partition(s)
-    order = kernel_order(s)
-    maxr = max(wr[w + 1] - wr[w] for w in range(NUM_WARPS))
-    maxt = max(wt[w + 1] - wt[w] for w in range(NUM_WARPS))
+    plan = outer_plan(s)
+    maxcell = max(1, max(len(c) for c in plan.cells))
     out = [f"// {note}", f"struct Spec{idx} {{",
            f"  static constexpr uint64_t KEY = {structure_key(s)}ull;",
            f"  static constexpr int T = {len(s.row)}, R = {s.num_rows}, DF = {s.d_feat}, DY = {s.d_y};",
-           f"  static constexpr int MAXR = {maxr}, MAXT = {((maxt + 3) // 4) * 4};",
-           f"  static constexpr int WT[{NUM_WARPS + 1}] = {{{', '.join(map(str, wt))}}};",
-           f"  static constexpr int WR[{NUM_WARPS + 1}] = {{{', '.join(map(str, wr))}}};"]
-    for w in range(NUM_WARPS):
-        out.append("  template <int CPL> __device__ __forceinline__ static void "
-                   f"segsum_w{w}(float (&acc)[MAXR][CPL], const float (&x)[DF][CPL], const float4* cf) {{")
-        out.append("    float4 c;")
-        out += _emit_segsum(s, order, wt, wr, w)
-        out.append("  }")
-        out.append("  template <int CPL> __device__ __forceinline__ static void "
-                   f"inner_w{w}(float (&ay)[DY], const float (&x)[DF][CPL], const float (&g)[MAXR][CPL], const float4* sc) {{")
-        out.append("    float4 c;")
-        out += _emit_inner(s, order, wt, wr, w)
-        out.append("  }")
+           f"  static constexpr int MAXCELL = {maxcell};",
+           f"  static constexpr int NCELL[{NUM_ROLES}] = {{{', '.join(str(len(c)) for c in plan.cells)}}};",
+           f"  static constexpr int OT1 = {plan.offsets[1]}, OT2 = {plan.offsets[2]};   // role 1's scales start at OT1"]
+    for w in range(NUM_ROLES):
+        out += _emit_outer_role(s, plan, w)
     out.append("};")
     return "\n".join(out)
 

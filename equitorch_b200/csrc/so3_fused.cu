@@ -9,14 +9,16 @@
 // respect to the harmonics.
 //
 // Two implementations of each:
-//  * "spec": for index structures unrolled at build time (generated/tp_specs.inc).  One CTA of
-//    four warps walks a contiguous range of destination nodes.  Feature rows of the next four
-//    edges are fetched with bulk asynchronous copies (cp.async.bulk + mbarrier, double
-//    buffered) while the current four are consumed.  Each warp owns a contiguous block of
-//    intermediate rows; a lane holds CPL channels of all D_feat gathered components and of its
-//    rows' accumulators in registers, the per-edge coefficients scale[t]*y[my[t]] are built
-//    by the warp in shared memory and read back as broadcast 128-bit loads.  No atomics: the
-//    edges of a node are consecutive, the accumulators are flushed once per node.
+//  * "spec": for index structures unrolled at build time (generated/tp_specs.inc).  The sum over
+//    the edges of a node commutes with the CG contraction, so per edge only the dense outer
+//    product Q[m_y, m_feat] += y_e[m_y] x_e[m_feat] is accumulated (234 of the 256 cells are used
+//    at l_max = 3) and the 353-entry sparse contraction runs once per node.  One CTA walks a
+//    contiguous range of destination nodes; feature rows of the next four edges are fetched with
+//    bulk asynchronous copies (cp.async.bulk + mbarrier, double buffered) while the current four
+//    are consumed.  A warp handles 32 channels (one per lane) and one half of the cells, chosen
+//    so that every intermediate row is produced by exactly one warp from its own registers.  No
+//    atomics: the edges of a node are consecutive.  The adjoint runs the same scheme backwards:
+//    H[cell] = sum_t scale[t] G_d[row(t)] once per node, then a dense dot product per edge.
 //  * "generic": table-driven, one thread per output element; any structure, any channel count.
 #include <algorithm>
 
@@ -24,27 +26,12 @@
 
 namespace eqt {
 namespace specs {
-#define EQT_FMA_ROW(ACC, A, X)                     \
-  do {                                             \
-    _Pragma("unroll") for (int k_ = 0; k_ < CPL; ++k_)(ACC)[k_] = fmaf((A), (X)[k_], (ACC)[k_]); \
-  } while (0)
-template <int CPL>
-__device__ __forceinline__ float dot_row(const float (&a)[CPL], const float (&b)[CPL]) {
-  float s = a[0] * b[0];
-#pragma unroll
-  for (int k = 1; k < CPL; ++k) s = fmaf(a[k], b[k], s);
-  return s;
-}
-#define EQT_DOT_ROW(X, G) dot_row<CPL>((X), (G))
 #include "generated/tp_specs.inc"
-#undef EQT_FMA_ROW
-#undef EQT_DOT_ROW
 }  // namespace specs
 
 namespace {
 
 constexpr int STAGES = 4;   // edges per batch
-constexpr int NW = 4;       // warps per CTA
 constexpr int WAIT_SPINS = 1 << 22;
 
 struct FusedArgs {
@@ -55,8 +42,7 @@ struct FusedArgs {
   const int64_t* ptr;       // (N + 1) CSR of edges per output node, or NULL (one edge per output)
   const int64_t* enode;     // (E) node of each edge (generic inner kernel only)
   const float* scale;       // (T)
-  const float* scale_k;     // (T) in the unrolled kernels' entry order, or NULL
-  const int64_t* my_k;      // (T) likewise
+  const float* scale_o;     // scales in the unrolled kernels' role order (zero padded), or NULL
   const int64_t* mf;        // (T)
   const int64_t* my;        // (T)
   const int64_t* rowptr;    // (R + 1)
@@ -100,64 +86,120 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
                : "memory");
 }
 __device__ __forceinline__ void cta_sync() { asm volatile("bar.sync 0;" ::: "memory"); }
-
-template <class S>
-__device__ __forceinline__ void warp_ranges(int w, int& tb, int& te, int& rb, int& re) {
-  tb = S::WT[0]; te = S::WT[1]; rb = S::WR[0]; re = S::WR[1];
-  if (w == 1) { tb = S::WT[1]; te = S::WT[2]; rb = S::WR[1]; re = S::WR[2]; }
-  if (w == 2) { tb = S::WT[2]; te = S::WT[3]; rb = S::WR[2]; re = S::WR[3]; }
-  if (w == 3) { tb = S::WT[3]; te = S::WT[4]; rb = S::WR[3]; re = S::WR[4]; }
+__device__ __forceinline__ void cp_async_4(void* dst_smem, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_addr(dst_smem)), "l"(src) : "memory");
+}
+// one arrival (already part of the barrier's init count) once this thread's earlier cp.async have landed
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
 
-template <class S, int CPL>
-constexpr size_t spec_smem_bytes() {
-  return sizeof(float) * (2 * STAGES * S::DF * 32 * CPL   // feature rows, two sets
-                          + 2 * NW * S::MAXT              // per-warp coefficients and scales
-                          + NW * STAGES * S::DY           // per-warp copy of the batch's harmonics
-                          + 2 * STAGES * NW * S::DY)      // inner: per-warp partial grad_y, two sets
-         + S::T                                           // my[] as bytes
-         + 64;
-}
-
-// Shared prologue: carve shared memory, stage the per-warp scale block and my[], init barriers.
-template <class S, int CPL>
+// Shared memory of the spec kernels for a CTA of NWARP warps and a ring of NS batches.
+template <class S, int CQ>
 struct Smem {
-  float* xs;
-  float* wbuf;    // [NW][MAXT] coefficients of the current edge
-  float* wsc;     // [NW][MAXT] scales of the warp's entries
-  float* wy;      // [NW][STAGES][DY]
-  float* red;     // [2][STAGES][NW][DY]
-  uint8_t* smy;   // [T]
+  static constexpr int C = 32 * CQ, NWARP = 2 * CQ, ROWF = S::DF * C;
+  static constexpr int NS = 6;    // batches in flight (ring of STAGES-edge sets); 4 KB rows at C = 64: 96 KB per CTA
+  float* xs;      // [NS][STAGES][DF * C] gathered feature rows
+  float* ys;      // [NS][STAGES][DY] harmonics rows of the batch (segment sum)
+  float* ssc;     // [OT2] scales in role order
+  float* red;     // [2][STAGES][NWARP][DY] per-warp partial grad_y, two sets (adjoint)
   __device__ explicit Smem(unsigned char* base) {
     xs = reinterpret_cast<float*>(base);
-    wbuf = xs + 2 * STAGES * S::DF * 32 * CPL;
-    wsc = wbuf + NW * S::MAXT;
-    wy = wsc + NW * S::MAXT;
-    red = wy + NW * STAGES * S::DY;
-    smy = reinterpret_cast<uint8_t*>(red + 2 * STAGES * NW * S::DY);
+    ys = xs + NS * STAGES * ROWF;
+    ssc = ys + NS * STAGES * S::DY;
+    red = ssc + S::OT2;
+  }
+  static constexpr size_t bytes() {
+    return sizeof(float) * (NS * STAGES * ROWF + NS * STAGES * S::DY + S::OT2 + 2 * STAGES * NWARP * S::DY) + 64;
   }
 };
 
-// ---- spec kernel: gather + CG + segment sum -----------------------------------------------------
-template <class S, int CPL>
-__global__ void __launch_bounds__(NW * 32, 4) tp_segsum_spec_kernel(FusedArgs a) {
-  constexpr int C = 32 * CPL, ROWF = S::DF * C;
-  constexpr uint32_t ROWB = ROWF * sizeof(float);
-  extern __shared__ __align__(128) unsigned char smem_raw[];
-  __shared__ uint64_t bars[2];
-  Smem<S, CPL> sm(smem_raw);
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  int tb, te, rb, re;
-  warp_ranges<S>(warp, tb, te, rb, re);
-  float* wcoef = sm.wbuf + warp * S::MAXT;
-  float* wscale = sm.wsc + warp * S::MAXT;
-  float* wys = sm.wy + warp * STAGES * S::DY;
+// Ring of edge batches filled NS - 1 batches ahead of their use by warp 0: feature rows by bulk copies
+// (lane s copies the row of edge s), harmonics elements by 4-byte cp.async, both completing on the
+// batch's mbarrier (1 arrival for the expected bytes + 1 per lane of warp 0 for its cp.async).  The
+// gather indices of a batch are read one iteration before they are needed, so no global-memory
+// latency sits between two batches.
+template <class S, int CQ, bool WITH_Y>
+struct EdgeRing {
+  using SM = Smem<S, CQ>;
+  static constexpr int NS = SM::NS, ROWF = SM::ROWF;
+  static constexpr uint32_t ROWB = ROWF * sizeof(float);
+  const FusedArgs& a;
+  SM& sm;
+  uint64_t* bars;
+  int64_t e0, e1, nb;
+  int warp, lane;
+  int64_t fi = 0, yi = 0;   // warp 0, lane s: indices of edge s of the next batch to issue
 
-  for (int t = tid; t < S::T; t += NW * 32) sm.smy[t] = static_cast<uint8_t>(__ldg(a.my_k + t));
-  for (int t = tb + lane; t < te; t += 32) wscale[t - tb] = __ldg(a.scale_k + t);
+  __device__ EdgeRing(const FusedArgs& a_, SM& sm_, uint64_t* bars_, int64_t e0_, int64_t e1_, int warp_, int lane_)
+      : a(a_), sm(sm_), bars(bars_), e0(e0_), e1(e1_), nb(ceil_div(e1_ - e0_, STAGES)), warp(warp_), lane(lane_) {}
+
+  __device__ void load_idx(int64_t bb) {
+    const int64_t e = e0 + bb * STAGES + lane;
+    if (lane < STAGES && e < e1) {
+      fi = a.fidx ? __ldg(a.fidx + e) : e;
+      if (WITH_Y) yi = a.yidx ? __ldg(a.yidx + e) : e;
+    }
+  }
+  __device__ void issue(int64_t bb) {   // whole warp 0; indices of batch bb are in fi / yi
+    const int set = (int)(bb % NS);
+    const int64_t eb = e0 + bb * STAGES;
+    const int cnt = (int)min((int64_t)STAGES, e1 - eb);
+    if (lane == 0) mbar_expect_tx(&bars[set], cnt * ROWB);
+    if (lane < cnt) bulk_load(sm.xs + (set * STAGES + lane) * ROWF, a.feat + fi * ROWF, ROWB, &bars[set]);
+    if (WITH_Y) {
+#pragma unroll
+      for (int i0 = 0; i0 < STAGES * S::DY; i0 += 32) {
+        const int i = i0 + lane, ed = min(i / S::DY, STAGES - 1);
+        const int64_t yrow = __shfl_sync(0xffffffffu, yi, ed);
+        if (i < cnt * S::DY) cp_async_4(sm.ys + set * STAGES * S::DY + i, a.y + yrow * S::DY + (i - ed * S::DY));
+      }
+    }
+    cp_async_arrive(&bars[set]);
+  }
+  __device__ void prologue() {
+    if (warp != 0) return;
+    for (int64_t bb = 0; bb < NS - 1 && bb < nb; ++bb) {
+      load_idx(bb);
+      issue(bb);
+    }
+    if (NS - 1 < nb) load_idx(NS - 1);
+  }
+  // start of iteration b (every warp has left batch b - 1, whose set is refilled now); returns false on a timeout
+  __device__ bool begin(int64_t b) {
+    if (warp == 0) {
+      const int64_t bb = b + NS - 1;
+      if (bb < nb) issue(bb);
+      if (bb + 1 < nb) load_idx(bb + 1);
+    }
+    return mbar_wait(&bars[b % NS], (uint32_t)((b / NS) & 1));
+  }
+  // after a timeout: give copies that may still be in flight a bounded chance to land before the CTA retires
+  __device__ void drain(int64_t b) {
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    for (int64_t bb = b; bb < nb && bb < b + NS - 1; ++bb) mbar_wait(&bars[bb % NS], (uint32_t)((bb / NS) & 1));
+  }
+};
+
+// ---- spec kernel: gather + outer product + per-node CG + segment sum ---------------------------------
+// Warp (cq, role): channels [32 cq, 32 cq + 32), one per lane; role selects the half of the (m_y, m_feat)
+// cells whose accumulators Q[cell] = sum_e y_e[m_y] x_e[m_feat] the warp keeps in registers.  When the
+// last edge of a node has been added the warp turns its Q into its share of the rows,
+// S[d, r] = sum_t scale[t] Q[cell(t)], stores them and clears Q.
+template <class S, int CQ>
+__global__ void __launch_bounds__(64 * CQ, 4 / CQ) tp_segsum_spec_kernel(FusedArgs a) {
+  using SM = Smem<S, CQ>;
+  constexpr int C = SM::C, ROWF = SM::ROWF, NT = 64 * CQ, NS = SM::NS;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ uint64_t bars[NS];
+  SM sm(smem_raw);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int role = warp & 1, ch = (warp >> 1) * 32 + lane;
+  const float4* sc = reinterpret_cast<const float4*>(sm.ssc + (role ? S::OT1 : 0));
+
+  for (int t = tid; t < S::OT2; t += NT) sm.ssc[t] = __ldg(a.scale_o + t);
   if (tid == 0) {
-    mbar_init(&bars[0], 1);
-    mbar_init(&bars[1], 1);
+    for (int i = 0; i < NS; ++i) mbar_init(&bars[i], 1 + 32);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   cta_sync();
@@ -166,90 +208,48 @@ __global__ void __launch_bounds__(NW * 32, 4) tp_segsum_spec_kernel(FusedArgs a)
   const int64_t d1 = min(d0 + a.nodes_per_cta, a.n_out);
   const int64_t e0 = a.ptr ? __ldg(a.ptr + d0) : d0;
   const int64_t e1 = a.ptr ? __ldg(a.ptr + d1) : d1;
-  const int64_t nb = ceil_div(e1 - e0, STAGES);
+  EdgeRing<S, CQ, true> ring(a, sm, bars, e0, e1, warp, lane);
+  ring.prologue();
 
-  auto issue = [&](int64_t b) {
-    if (tid == 0) {
-      const int set = b & 1;
-      const int64_t eb = e0 + b * STAGES;
-      const int cnt = (int)min((int64_t)STAGES, e1 - eb);
-      mbar_expect_tx(&bars[set], cnt * ROWB);
-      for (int s = 0; s < cnt; ++s) {
-        const int64_t row = a.fidx ? __ldg(a.fidx + eb + s) : eb + s;
-        bulk_load(sm.xs + (set * STAGES + s) * ROWF, a.feat + row * ROWF, ROWB, &bars[set]);
-      }
-    }
-  };
-
-  float acc[S::MAXR][CPL];
+  float q[S::MAXCELL];
 #pragma unroll
-  for (int r = 0; r < S::MAXR; ++r)
-#pragma unroll
-    for (int k = 0; k < CPL; ++k) acc[r][k] = 0.f;
+  for (int i = 0; i < S::MAXCELL; ++i) q[i] = 0.f;
 
   int64_t d_cur = d0;
   int64_t boundary = a.ptr ? __ldg(a.ptr + d_cur + 1) : d_cur + 1;
-  auto flush = [&]() {
-    float* o = a.out + (d_cur * S::R + rb) * C + lane * CPL;
+  auto flush = [&]() {   // a node without edges flushes a zero Q, i.e. zero rows
+    float* o = a.out + d_cur * S::R * C + ch;
+    if (role == 0) S::template node_r0<C>(q, sc, o);
+    else S::template node_r1<C>(q, sc, o);
 #pragma unroll
-    for (int r = 0; r < S::MAXR; ++r) {
-      if (r < re - rb) {
-        if (CPL == 2) *reinterpret_cast<float2*>(o + r * C) = make_float2(acc[r][0], acc[r][CPL - 1]);
-        else o[r * C] = acc[r][0];
-      }
-#pragma unroll
-      for (int k = 0; k < CPL; ++k) acc[r][k] = 0.f;
-    }
+    for (int i = 0; i < S::MAXCELL; ++i) q[i] = 0.f;
     ++d_cur;
     if (d_cur < d1) boundary = a.ptr ? __ldg(a.ptr + d_cur + 1) : d_cur + 1;
   };
 
-  bool failed = false;
-  if (nb > 0) issue(0);
-  for (int64_t b = 0; b < nb; ++b) {
-    if (b + 1 < nb) issue(b + 1);
-    const int set = b & 1;
+  for (int64_t b = 0; b < ring.nb; ++b) {
+    if (!ring.begin(b)) {
+      if (tid == 0) atomicExch(a.status, 1);
+      ring.drain(b);
+      return;
+    }
+    const int set = (int)(b % NS);
     const int64_t eb = e0 + b * STAGES;
     const int cnt = (int)min((int64_t)STAGES, e1 - eb);
-    // the warp's own copy of the batch's harmonics (requested before waiting for the feature rows)
-    for (int q = lane; q < cnt * S::DY; q += 32) {
-      const int64_t e = eb + q / S::DY;
-      wys[q] = __ldg(a.y + (a.yidx ? __ldg(a.yidx + e) : e) * S::DY + q % S::DY);
-    }
-    if (!mbar_wait(&bars[set], (b >> 1) & 1)) { failed = true; break; }
-    __syncwarp();
     for (int s = 0; s < cnt; ++s) {
       const int64_t e = eb + s;
       while (e >= boundary) flush();
-      const float* ye = wys + s * S::DY;
-      for (int t = tb + lane; t < te; t += 32) wcoef[t - tb] = wscale[t - tb] * ye[sm.smy[t]];
-      __syncwarp();
-      float x[S::DF][CPL];
-      const float* xr = sm.xs + (set * STAGES + s) * ROWF + lane * CPL;
+      float x[S::DF], yv[S::DY];
+      const float* xr = sm.xs + (set * STAGES + s) * ROWF + ch;
+      const float* yr = sm.ys + (set * STAGES + s) * S::DY;
 #pragma unroll
-      for (int m = 0; m < S::DF; ++m) {
-        if (CPL == 2) {
-          const float2 v = *reinterpret_cast<const float2*>(xr + m * C);
-          x[m][0] = v.x; x[m][CPL - 1] = v.y;
-        } else {
-          x[m][0] = xr[m * C];
-        }
-      }
-      const float4* cf = reinterpret_cast<const float4*>(wcoef);
-      if (warp == 0) S::template segsum_w0<CPL>(acc, x, cf);
-      else if (warp == 1) S::template segsum_w1<CPL>(acc, x, cf);
-      else if (warp == 2) S::template segsum_w2<CPL>(acc, x, cf);
-      else S::template segsum_w3<CPL>(acc, x, cf);
-      __syncwarp();
+      for (int m = 0; m < S::DF; ++m) x[m] = xr[m * C];
+#pragma unroll
+      for (int k = 0; k < S::DY; ++k) yv[k] = yr[k];
+      if (role == 0) S::outer_r0(q, x, yv);
+      else S::outer_r1(q, x, yv);
     }
     cta_sync();   // everybody is done with this set before it is refilled
-  }
-  if (failed) {
-    if (tid == 0) atomicExch(a.status, 1);
-    // give copies that may still be in flight a bounded chance to land before the CTA retires
-    mbar_wait(&bars[0], 0);
-    mbar_wait(&bars[1], 0);
-    return;
   }
   while (d_cur < d1) flush();
 }
@@ -283,21 +283,21 @@ __device__ __forceinline__ void warp_reduce_to_smem(float (&v)[N], float* dst, i
 }
 
 // ---- spec kernel: adjoint w.r.t. the channel-less operand ----------------------------------------
-template <class S, int CPL>
-__global__ void __launch_bounds__(NW * 32, 4) tp_inner_spec_kernel(FusedArgs a) {
-  constexpr int C = 32 * CPL, ROWF = S::DF * C;
-  constexpr uint32_t ROWB = ROWF * sizeof(float);
+// gy_e[k] = sum_{cells (k, m)} sum_c x_e[m, c] H_d[cell, c]  with  H_d[cell] = sum_{t in cell} scale[t] G_d[row(t)]
+// built once per node in registers (same warp roles as above), then one dense dot product per edge.
+template <class S, int CQ>
+__global__ void __launch_bounds__(64 * CQ, 4 / CQ) tp_inner_spec_kernel(FusedArgs a) {
+  using SM = Smem<S, CQ>;
+  constexpr int C = SM::C, ROWF = SM::ROWF, NT = 64 * CQ, NWARP = SM::NWARP, NS = SM::NS;
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  __shared__ uint64_t bars[2];
-  Smem<S, CPL> sm(smem_raw);
+  __shared__ uint64_t bars[NS];
+  SM sm(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  int tb, te, rb, re;
-  warp_ranges<S>(warp, tb, te, rb, re);
-  float* wscale = sm.wbuf + warp * S::MAXT;
-  for (int t = tb + lane; t < te; t += 32) wscale[t - tb] = __ldg(a.scale_k + t);
+  const int role = warp & 1, ch = (warp >> 1) * 32 + lane;
+  const float4* sc = reinterpret_cast<const float4*>(sm.ssc + (role ? S::OT1 : 0));
+  for (int t = tid; t < S::OT2; t += NT) sm.ssc[t] = __ldg(a.scale_o + t);
   if (tid == 0) {
-    mbar_init(&bars[0], 1);
-    mbar_init(&bars[1], 1);
+    for (int i = 0; i < NS; ++i) mbar_init(&bars[i], 1 + 32);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   cta_sync();
@@ -305,91 +305,59 @@ __global__ void __launch_bounds__(NW * 32, 4) tp_inner_spec_kernel(FusedArgs a) 
   const int64_t d0 = (int64_t)blockIdx.x * a.nodes_per_cta;
   const int64_t d1 = min(d0 + a.nodes_per_cta, a.n_out);
   const int64_t e0 = __ldg(a.ptr + d0), e1 = __ldg(a.ptr + d1);
-  const int64_t nb = ceil_div(e1 - e0, STAGES);
+  EdgeRing<S, CQ, false> ring(a, sm, bars, e0, e1, warp, lane);
+  ring.prologue();
 
-  auto issue = [&](int64_t b) {
-    if (tid == 0) {
-      const int set = b & 1;
-      const int64_t eb = e0 + b * STAGES;
-      const int cnt = (int)min((int64_t)STAGES, e1 - eb);
-      mbar_expect_tx(&bars[set], cnt * ROWB);
-      for (int s = 0; s < cnt; ++s) {
-        const int64_t row = a.fidx ? __ldg(a.fidx + eb + s) : eb + s;
-        bulk_load(sm.xs + (set * STAGES + s) * ROWF, a.feat + row * ROWF, ROWB, &bars[set]);
-      }
-    }
-  };
-
-  float g[S::MAXR][CPL];
+  float h[S::MAXCELL];
+#pragma unroll
+  for (int i = 0; i < S::MAXCELL; ++i) h[i] = 0.f;
   int64_t d_cur = d0 - 1;
-  int64_t boundary = e0;   // forces a load of G for the first node that has an edge
+  int64_t boundary = e0;   // forces H to be built for the first node that has an edge
   auto next_node = [&]() {
     ++d_cur;
     boundary = __ldg(a.ptr + d_cur + 1);
-    const float* gp = a.g + (d_cur * S::R + rb) * C + lane * CPL;
-#pragma unroll
-    for (int r = 0; r < S::MAXR; ++r) {
-      if (r < re - rb) {
-        if (CPL == 2) {
-          const float2 v = __ldg(reinterpret_cast<const float2*>(gp + r * C));
-          g[r][0] = v.x; g[r][CPL - 1] = v.y;
-        } else {
-          g[r][0] = __ldg(gp + r * C);
-        }
-      } else {
-#pragma unroll
-        for (int k = 0; k < CPL; ++k) g[r][k] = 0.f;
-      }
+    if (boundary > __ldg(a.ptr + d_cur)) {
+      const float* gp = a.g + d_cur * S::R * C + ch;
+      if (role == 0) S::template hbuild_r0<C>(h, sc, gp);
+      else S::template hbuild_r1<C>(h, sc, gp);
     }
   };
 
-  bool failed = false;
-  if (nb > 0) issue(0);
-  for (int64_t b = 0; b < nb; ++b) {
-    if (b + 1 < nb) issue(b + 1);
-    const int set = b & 1;
-    if (!mbar_wait(&bars[set], (b >> 1) & 1)) { failed = true; break; }
+  for (int64_t b = 0; b < ring.nb; ++b) {
+    if (!ring.begin(b)) {
+      if (tid == 0) atomicExch(a.status, 1);
+      ring.drain(b);
+      return;
+    }
+    const int set = (int)(b % NS), rset = (int)(b & 1);
     const int64_t eb = e0 + b * STAGES;
     const int cnt = (int)min((int64_t)STAGES, e1 - eb);
     for (int s = 0; s < cnt; ++s) {
       const int64_t e = eb + s;
       while (e >= boundary) next_node();
-      float x[S::DF][CPL];
-      const float* xr = sm.xs + (set * STAGES + s) * ROWF + lane * CPL;
+      float x[S::DF];
+      const float* xr = sm.xs + (set * STAGES + s) * ROWF + ch;
 #pragma unroll
-      for (int m = 0; m < S::DF; ++m) {
-        if (CPL == 2) {
-          const float2 v = *reinterpret_cast<const float2*>(xr + m * C);
-          x[m][0] = v.x; x[m][CPL - 1] = v.y;
-        } else {
-          x[m][0] = xr[m * C];
-        }
-      }
+      for (int m = 0; m < S::DF; ++m) x[m] = xr[m * C];
       float ay[S::DY];
 #pragma unroll
       for (int k = 0; k < S::DY; ++k) ay[k] = 0.f;
-      const float4* sc = reinterpret_cast<const float4*>(wscale);
-      if (warp == 0) S::template inner_w0<CPL>(ay, x, g, sc);
-      else if (warp == 1) S::template inner_w1<CPL>(ay, x, g, sc);
-      else if (warp == 2) S::template inner_w2<CPL>(ay, x, g, sc);
-      else S::template inner_w3<CPL>(ay, x, g, sc);
-      float* rd = sm.red + ((set * STAGES + s) * NW + warp) * S::DY;
+      if (role == 0) S::dot_r0(ay, x, h);
+      else S::dot_r1(ay, x, h);
+      float* rd = sm.red + ((rset * STAGES + s) * NWARP + warp) * S::DY;
       warp_reduce_to_smem<S::DY>(ay, rd, lane);
     }
     cta_sync();
-    // combine the four warps' partial sums of this batch; the other set is free until the next sync
-    for (int q = tid; q < cnt * S::DY; q += NW * 32) {
-      const int s = q / S::DY, k = q % S::DY;
-      const float* rd = sm.red + ((set * STAGES + s) * NW) * S::DY + k;
-      const float v = (rd[0] + rd[S::DY]) + (rd[2 * S::DY] + rd[3 * S::DY]);
+    // combine the warps' partial sums of this batch; the other set of partial sums is free until the next sync
+    for (int i = tid; i < cnt * S::DY; i += NT) {
+      const int s = i / S::DY, k = i % S::DY;
+      const float* rd = sm.red + ((rset * STAGES + s) * NWARP) * S::DY + k;
+      float v = rd[0];
+#pragma unroll
+      for (int w = 1; w < NWARP; ++w) v += rd[w * S::DY];
       const int64_t e = eb + s;
       a.out[(a.yidx ? __ldg(a.yidx + e) : e) * S::DY + k] = v;
     }
-  }
-  if (failed) {
-    if (tid == 0) atomicExch(a.status, 1);
-    mbar_wait(&bars[0], 0);
-    mbar_wait(&bars[1], 0);
   }
 }
 
@@ -444,10 +412,10 @@ __global__ void __launch_bounds__(128) tp_inner_generic_kernel(FusedArgs a) {
 }
 
 // ---- dispatch ------------------------------------------------------------------------------------
-template <class S, int CPL>
+template <class S, int CQ>
 int launch_spec(bool inner, const FusedArgs& a, cudaStream_t s) {
-  constexpr size_t bytes = spec_smem_bytes<S, CPL>();
-  auto kern = inner ? tp_inner_spec_kernel<S, CPL> : tp_segsum_spec_kernel<S, CPL>;
+  constexpr size_t bytes = Smem<S, CQ>::bytes();
+  auto kern = inner ? tp_inner_spec_kernel<S, CQ> : tp_segsum_spec_kernel<S, CQ>;
   static bool configured[2] = {false, false};
   if (!configured[inner]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
@@ -455,13 +423,14 @@ int launch_spec(bool inner, const FusedArgs& a, cudaStream_t s) {
     configured[inner] = true;
   }
   const unsigned grid = (unsigned)ceil_div(a.n_out, a.nodes_per_cta);
-  kern<<<grid, NW * 32, bytes, s>>>(a);
+  kern<<<grid, 64 * CQ, bytes, s>>>(a);
   return check_launch(inner ? "tp_inner_spec_kernel" : "tp_segsum_spec_kernel");
 }
 
 template <class S>
 bool try_spec(uint64_t key, bool inner, const FusedArgs& a, cudaStream_t s, int& rc) {
   if (key != S::KEY || a.T != S::T || a.R != S::R || a.DF != S::DF || a.DY != S::DY) return false;
+  if (a.C == 128) { rc = launch_spec<S, 4>(inner, a, s); return true; }
   if (a.C == 64) { rc = launch_spec<S, 2>(inner, a, s); return true; }
   if (a.C == 32) { rc = launch_spec<S, 1>(inner, a, s); return true; }
   return false;
@@ -469,7 +438,7 @@ bool try_spec(uint64_t key, bool inner, const FusedArgs& a, cudaStream_t s, int&
 
 int run(bool inner, const eqt_tp_table* tab, FusedArgs a, cudaStream_t s) {
   if (a.n_out == 0 || (inner && a.n_edges == 0)) return EQT_OK;
-  if ((reinterpret_cast<uintptr_t>(a.feat) & 15u) == 0 && a.status && a.scale_k && a.my_k && (!inner || a.ptr)) {
+  if ((reinterpret_cast<uintptr_t>(a.feat) & 15u) == 0 && a.status && a.scale_o && (!inner || a.ptr)) {
     // nodes per CTA: keep every SM busy with several CTAs but amortise the pipeline prologue
     int64_t per = std::max<int64_t>(1, a.n_out / (148 * 16));
     const int64_t avg_deg = std::max<int64_t>(1, a.n_edges / std::max<int64_t>(1, a.n_out));
@@ -496,7 +465,7 @@ int fill(const eqt_tp_table* tab, FusedArgs& a) {
   if (tab->num_entries < 0 || tab->num_rows < 0 || tab->d_feat <= 0 || tab->d_y <= 0 || tab->d_y > 255)
     return fail(EQT_ERR_BAD_ARGUMENT, "bad table sizes");
   a.scale = tab->scale; a.mf = tab->m_feat; a.my = tab->m_y; a.rowptr = tab->row_ptr;
-  a.scale_k = tab->scale_k; a.my_k = tab->m_y_k;
+  a.scale_o = tab->scale_o;
   a.T = tab->num_entries; a.R = tab->num_rows; a.DF = tab->d_feat; a.DY = tab->d_y;
   return EQT_OK;
 }

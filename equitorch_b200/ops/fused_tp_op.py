@@ -14,7 +14,7 @@ import torch
 from torch import Tensor
 
 from .. import _lib
-from ..csrc.gen_tp_specs import kernel_order, structure_from_info, structure_key
+from ..csrc.gen_tp_specs import outer_order, structure_from_info, structure_key
 from ..structs import SparseProductInfo
 
 _status: Dict[torch.device, Tensor] = {}
@@ -49,12 +49,11 @@ class TpTable:
         self.row_ptr = torch.from_numpy(rowptr).to(device)
         self.num_entries, self.num_rows, self.d_feat, self.d_y = len(s.mf), s.num_rows, d_feat, d_y
         self.device = torch.device(device)
-        order = torch.from_numpy(kernel_order(s).astype(np.int64)).to(device)
-        self.scale_k = self.scale.index_select(0, order).contiguous()
-        self.m_y_k = self.m_y.index_select(0, order).contiguous()
+        order = torch.from_numpy(outer_order(s)).to(device)
+        self.scale_o = torch.where(order >= 0, self.scale[order.clamp_min(0)], self.scale.new_zeros(())).contiguous()
         self.struct = _lib.TpTableStruct(self.scale.data_ptr(), self.m_feat.data_ptr(), self.m_y.data_ptr(),
                                          self.row_ptr.data_ptr(), self.num_entries, self.num_rows, d_feat, d_y, self.key,
-                                         self.scale_k.data_ptr(), self.m_y_k.data_ptr())
+                                         self.scale_o.data_ptr())
         self.tc_struct = self._merged(s, device)
 
     def _merged(self, s, device):

@@ -146,8 +146,8 @@ typedef struct eqt_tp_table {
   int32_t d_feat;           /* components of the channelled operand                   */
   int32_t d_y;              /* components of the channel-less operand (<= 255)        */
   uint64_t structure_key;
-  const float* scale_k;     /* (T,) scale permuted into the unrolled kernels' entry order, or NULL */
-  const int64_t* m_y_k;     /* (T,) m_y in the same order, or NULL (then only table-driven kernels run) */
+  const float* scale_o;     /* scale permuted into the unrolled kernels' role order (zero padded; see
+                               gen_tp_specs.outer_order), or NULL (then only table-driven kernels run) */
 } eqt_tp_table;
 
 /*
