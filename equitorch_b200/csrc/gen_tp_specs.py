@@ -62,7 +62,7 @@ def structure_from_info(info, feat_is_input1: bool, d_feat: int, d_y: int) -> St
     return Structure(mf.astype(np.int64), my.astype(np.int64), row.astype(np.int64), d_feat, d_y, info.out_size)
 
 
-NUM_ROLES = 2
+NUM_ROLES = 4
 
 
 class OuterPlan(NamedTuple):
@@ -133,17 +133,27 @@ def outer_order(s: Structure) -> np.ndarray:
 
 
 def _emit_outer_role(s: Structure, plan: OuterPlan, w: int) -> List[str]:
+    """Functions of warp role ``w``.  A lane holds CPL channels; ``xr`` points at its channels of the
+    staged feature row (component stride C floats), loaded component by component just before use."""
     cells, tw = plan.cells[w], plan.entries[w]
     index = {(int(k), int(m)): i for i, (k, m) in enumerate(cells)}
+    by_m = {}
+    for i, (k, m) in enumerate(cells):
+        by_m.setdefault(int(m), []).append((i, int(k)))
     out = []
     # per edge: q[cell] += x[m_feat] * y[m_y]
-    out.append(f"  __device__ __forceinline__ static void outer_r{w}(float (&q)[MAXCELL], const float (&x)[DF], const float (&y)[DY]) {{")
-    for i, (k, m) in enumerate(cells):
-        out.append(f"    q[{i}] = fmaf(x[{int(m)}], y[{int(k)}], q[{i}]);")
+    out.append("  template <int CPL, int C> __device__ __forceinline__ static void "
+               f"outer_r{w}(float (&q)[MAXCELL][CPL], const float* xr, const float (&y)[DY]) {{")
+    out.append("    float x[CPL];")
+    for m in sorted(by_m):
+        out.append(f"    EQT_LDX(x, xr + {m} * C);")
+        for i, k in by_m[m]:
+            out.append(f"    EQT_FMA(q[{i}], x, y[{k}]);")
     out.append("  }")
     # per node: rows of this role from the accumulators
-    out.append(f"  template <int CS> __device__ __forceinline__ static void node_r{w}(const float (&q)[MAXCELL], const float4* sc, float* o) {{")
-    out.append("    float4 c; float v;")
+    out.append("  template <int CPL, int C> __device__ __forceinline__ static void "
+               f"node_r{w}(const float (&q)[MAXCELL][CPL], const float4* sc, float* o) {{")
+    out.append("    float4 c; float v[CPL];")
     pos = {int(t): i for i, t in enumerate(tw)}
     by_row = {}
     for t in tw:
@@ -152,7 +162,7 @@ def _emit_outer_role(s: Structure, plan: OuterPlan, w: int) -> List[str]:
     for r in plan.rows[w]:
         ts = by_row.get(int(r), [])
         if not ts:
-            out.append(f"    o[{int(r)} * CS] = 0.f;")
+            out.append(f"    EQT_ZERO(v); EQT_STX(o + {int(r)} * C, v);")
             continue
         for n, t in enumerate(ts):
             i = pos[t]
@@ -161,19 +171,20 @@ def _emit_outer_role(s: Structure, plan: OuterPlan, w: int) -> List[str]:
                 out.append(f"    c = sc[{loaded}];")
             term = f"c.{'xyzw'[i % 4]}"
             cell = index[(int(s.my[t]), int(s.mf[t]))]
-            out.append(f"    v = {term} * q[{cell}];" if n == 0 else f"    v = fmaf({term}, q[{cell}], v);")
-        out.append(f"    o[{int(r)} * CS] = v;")
+            out.append(f"    EQT_MUL(v, q[{cell}], {term});" if n == 0 else f"    EQT_FMA(v, q[{cell}], {term});")
+        out.append(f"    EQT_STX(o + {int(r)} * C, v);")
     out.append("  }")
     # adjoint, per node: h[cell] = sum_t scale[t] * g[row[t]]
-    out.append(f"  template <int CS> __device__ __forceinline__ static void hbuild_r{w}(float (&h)[MAXCELL], const float4* sc, const float* g) {{")
-    out.append("    float4 c; float gr;")
+    out.append("  template <int CPL, int C> __device__ __forceinline__ static void "
+               f"hbuild_r{w}(float (&h)[MAXCELL][CPL], const float4* sc, const float* g) {{")
+    out.append("    float4 c; float gr[CPL];")
     touched = set()
     loaded = -1
     for r in plan.rows[w]:
         ts = by_row.get(int(r), [])
         if not ts:
             continue
-        out.append(f"    gr = g[{int(r)} * CS];")
+        out.append(f"    EQT_LDG(gr, g + {int(r)} * C);")
         for t in ts:
             i = pos[t]
             if i // 4 != loaded:
@@ -182,15 +193,19 @@ def _emit_outer_role(s: Structure, plan: OuterPlan, w: int) -> List[str]:
             term = f"c.{'xyzw'[i % 4]}"
             cell = index[(int(s.my[t]), int(s.mf[t]))]
             if cell in touched:
-                out.append(f"    h[{cell}] = fmaf({term}, gr, h[{cell}]);")
+                out.append(f"    EQT_FMA(h[{cell}], gr, {term});")
             else:
                 touched.add(cell)
-                out.append(f"    h[{cell}] = {term} * gr;")
+                out.append(f"    EQT_MUL(h[{cell}], gr, {term});")
     out.append("  }")
-    # adjoint, per edge: ay[m_y] += x[m_feat] * h[cell]
-    out.append(f"  __device__ __forceinline__ static void dot_r{w}(float (&ay)[DY], const float (&x)[DF], const float (&h)[MAXCELL]) {{")
-    for i, (k, m) in enumerate(cells):
-        out.append(f"    ay[{int(k)}] = fmaf(x[{int(m)}], h[{i}], ay[{int(k)}]);")
+    # adjoint, per edge: ay[m_y] += <x[m_feat], h[cell]> over the lane's channels
+    out.append("  template <int CPL, int C> __device__ __forceinline__ static void "
+               f"dot_r{w}(float (&ay)[DY], const float* xr, const float (&h)[MAXCELL][CPL]) {{")
+    out.append("    float x[CPL];")
+    for m in sorted(by_m):
+        out.append(f"    EQT_LDX(x, xr + {m} * C);")
+        for i, k in by_m[m]:
+            out.append(f"    EQT_DOT(ay[{k}], x, h[{i}]);")
     out.append("  }")
     return out
 
@@ -203,7 +218,8 @@ def emit_spec(idx: int, s: Structure, note: str) -> str:
            f"  static constexpr int T = {len(s.row)}, R = {s.num_rows}, DF = {s.d_feat}, DY = {s.d_y};",
            f"  static constexpr int MAXCELL = {maxcell};",
            f"  static constexpr int NCELL[{NUM_ROLES}] = {{{', '.join(str(len(c)) for c in plan.cells)}}};",
-           f"  static constexpr int OT1 = {plan.offsets[1]}, OT2 = {plan.offsets[2]};   // role 1's scales start at OT1"]
+           "  // start of each role's block in the permuted scale array, and its end",
+           "  static constexpr int " + ", ".join(f"OT{w} = {o}" for w, o in enumerate(plan.offsets)) + ";"]
     for w in range(NUM_ROLES):
         out += _emit_outer_role(s, plan, w)
     out.append("};")

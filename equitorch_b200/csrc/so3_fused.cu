@@ -15,8 +15,9 @@
 //    at l_max = 3) and the 353-entry sparse contraction runs once per node.  One CTA walks a
 //    contiguous range of destination nodes; feature rows of the next four edges are fetched with
 //    bulk asynchronous copies (cp.async.bulk + mbarrier, double buffered) while the current four
-//    are consumed.  A warp handles 32 channels (one per lane) and one half of the cells, chosen
-//    so that every intermediate row is produced by exactly one warp from its own registers.  No
+//    are consumed.  A warp handles 32 or 64 channels (one or two per lane) and one quarter of the
+//    cells, chosen so that every intermediate row is produced by exactly one warp from its own
+//    registers.  No
 //    atomics: the edges of a node are consecutive.  The adjoint runs the same scheme backwards:
 //    H[cell] = sum_t scale[t] G_d[row(t)] once per node, then a dense dot product per edge.
 //  * "generic": table-driven, one thread per output element; any structure, any channel count.
@@ -26,7 +27,33 @@
 
 namespace eqt {
 namespace specs {
+template <int CPL> __device__ __forceinline__ void ld_lane(float (&x)[CPL], const float* p) {
+  if constexpr (CPL == 2) { const float2 v = *reinterpret_cast<const float2*>(p); x[0] = v.x; x[1] = v.y; }
+  else x[0] = p[0];
+}
+template <int CPL> __device__ __forceinline__ void ldg_lane(float (&x)[CPL], const float* p) {
+  if constexpr (CPL == 2) { const float2 v = __ldg(reinterpret_cast<const float2*>(p)); x[0] = v.x; x[1] = v.y; }
+  else x[0] = __ldg(p);
+}
+template <int CPL> __device__ __forceinline__ void st_lane(float* p, const float (&v)[CPL]) {
+  if constexpr (CPL == 2) *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]);
+  else p[0] = v[0];
+}
+#define EQT_LDX(X, P) ld_lane<CPL>(X, P)
+#define EQT_LDG(X, P) ldg_lane<CPL>(X, P)
+#define EQT_STX(P, V) st_lane<CPL>(P, V)
+#define EQT_FMA(ACC, A, S) do { _Pragma("unroll") for (int k_ = 0; k_ < CPL; ++k_) (ACC)[k_] = fmaf((A)[k_], (S), (ACC)[k_]); } while (0)
+#define EQT_MUL(ACC, A, S) do { _Pragma("unroll") for (int k_ = 0; k_ < CPL; ++k_) (ACC)[k_] = (A)[k_] * (S); } while (0)
+#define EQT_ZERO(V) do { _Pragma("unroll") for (int k_ = 0; k_ < CPL; ++k_) (V)[k_] = 0.f; } while (0)
+#define EQT_DOT(ACC, X, H) do { _Pragma("unroll") for (int k_ = 0; k_ < CPL; ++k_) (ACC) = fmaf((X)[k_], (H)[k_], (ACC)); } while (0)
 #include "generated/tp_specs.inc"
+#undef EQT_LDX
+#undef EQT_LDG
+#undef EQT_STX
+#undef EQT_FMA
+#undef EQT_MUL
+#undef EQT_ZERO
+#undef EQT_DOT
 }  // namespace specs
 
 namespace {
@@ -58,6 +85,9 @@ struct FusedArgs {
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
@@ -94,59 +124,75 @@ __device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
 
-// Shared memory of the spec kernels for a CTA of NWARP warps and a ring of NS batches.
-template <class S, int CQ>
+// Shared memory of the spec kernels: a lane holds CPL channels, a CTA has CG groups of four warps (one
+// warp per role), i.e. C = 32 CPL CG channels, and a ring of NS batches of STAGES edges.
+template <class S, int CPL, int CG>
 struct Smem {
-  static constexpr int C = 32 * CQ, NWARP = 2 * CQ, ROWF = S::DF * C;
-  static constexpr int NS = 6;    // batches in flight (ring of STAGES-edge sets); 4 KB rows at C = 64: 96 KB per CTA
+  static constexpr int C = 32 * CPL * CG, NWARP = 4 * CG, NT = 32 * NWARP, ROWF = S::DF * C;
+  static constexpr int NS = 4;
   float* xs;      // [NS][STAGES][DF * C] gathered feature rows
   float* ys;      // [NS][STAGES][DY] harmonics rows of the batch (segment sum)
-  float* ssc;     // [OT2] scales in role order
+  float* ssc;     // [OT4] scales in role order
   float* red;     // [2][STAGES][NWARP][DY] per-warp partial grad_y, two sets (adjoint)
   __device__ explicit Smem(unsigned char* base) {
     xs = reinterpret_cast<float*>(base);
     ys = xs + NS * STAGES * ROWF;
     ssc = ys + NS * STAGES * S::DY;
-    red = ssc + S::OT2;
+    red = ssc + S::OT4;
   }
   static constexpr size_t bytes() {
-    return sizeof(float) * (NS * STAGES * ROWF + NS * STAGES * S::DY + S::OT2 + 2 * STAGES * NWARP * S::DY) + 64;
+    return sizeof(float) * (NS * STAGES * ROWF + NS * STAGES * S::DY + S::OT4 + 2 * STAGES * NWARP * S::DY) + 64;
   }
 };
 
-// Ring of edge batches filled NS - 1 batches ahead of their use by warp 0: feature rows by bulk copies
-// (lane s copies the row of edge s), harmonics elements by 4-byte cp.async, both completing on the
-// batch's mbarrier (1 arrival for the expected bytes + 1 per lane of warp 0 for its cp.async).  The
-// gather indices of a batch are read one iteration before they are needed, so no global-memory
-// latency sits between two batches.
-template <class S, int CQ, bool WITH_Y>
+// Ring of edge batches filled ahead of their use by warp 0: feature rows by bulk copies (lane s copies
+// the row of edge s), harmonics elements by 4-byte cp.async, both completing on the batch's "full"
+// mbarrier (1 arrival for the expected bytes + 1 per lane of warp 0 for its cp.async).  The gather
+// indices of a batch are read one iteration before they are needed, so no global-memory latency
+// sits between two batches.
+//   SYNCED:  the kernel ends every batch with a CTA barrier; batch b + NS - 1 is issued at the start of
+//            iteration b into the set batch b - 1 has just left.
+//   !SYNCED: warps run free; each releases a batch on its "empty" mbarrier, and batch b + NS - 2 is issued
+//            at the start of warp 0's iteration b once every warp has released batch b - 2.
+template <class S, int CPL, int CG, bool WITH_Y, bool SYNCED>
 struct EdgeRing {
-  using SM = Smem<S, CQ>;
-  static constexpr int NS = SM::NS, ROWF = SM::ROWF;
+  using SM = Smem<S, CPL, CG>;
+  static constexpr int NS = SM::NS, ROWF = SM::ROWF, LEAD = SYNCED ? NS - 1 : NS - 2;
   static constexpr uint32_t ROWB = ROWF * sizeof(float);
   const FusedArgs& a;
   SM& sm;
-  uint64_t* bars;
-  int64_t e0, e1, nb;
+  uint64_t* full;
+  uint64_t* empty;
+  int64_t e0;               // first edge of the CTA; everything else counts edges / batches from here in 32 bits
+  int ne, nb;
   int warp, lane;
   int64_t fi = 0, yi = 0;   // warp 0, lane s: indices of edge s of the next batch to issue
 
-  __device__ EdgeRing(const FusedArgs& a_, SM& sm_, uint64_t* bars_, int64_t e0_, int64_t e1_, int warp_, int lane_)
-      : a(a_), sm(sm_), bars(bars_), e0(e0_), e1(e1_), nb(ceil_div(e1_ - e0_, STAGES)), warp(warp_), lane(lane_) {}
+  __device__ EdgeRing(const FusedArgs& a_, SM& sm_, uint64_t* full_, uint64_t* empty_, int64_t e0_, int ne_,
+                      int warp_, int lane_)
+      : a(a_), sm(sm_), full(full_), empty(empty_), e0(e0_), ne(ne_), nb((ne_ + STAGES - 1) / STAGES), warp(warp_),
+        lane(lane_) {}
 
-  __device__ void load_idx(int64_t bb) {
-    const int64_t e = e0 + bb * STAGES + lane;
-    if (lane < STAGES && e < e1) {
+  __device__ static void init(uint64_t* full_, uint64_t* empty_) {   // one thread
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(&full_[i], 1 + 32);
+      mbar_init(&empty_[i], SM::NWARP);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __device__ void load_idx(int bb) {
+    const int er = bb * STAGES + lane;
+    if (lane < STAGES && er < ne) {
+      const int64_t e = e0 + er;
       fi = a.fidx ? __ldg(a.fidx + e) : e;
       if (WITH_Y) yi = a.yidx ? __ldg(a.yidx + e) : e;
     }
   }
-  __device__ void issue(int64_t bb) {   // whole warp 0; indices of batch bb are in fi / yi
-    const int set = (int)(bb % NS);
-    const int64_t eb = e0 + bb * STAGES;
-    const int cnt = (int)min((int64_t)STAGES, e1 - eb);
-    if (lane == 0) mbar_expect_tx(&bars[set], cnt * ROWB);
-    if (lane < cnt) bulk_load(sm.xs + (set * STAGES + lane) * ROWF, a.feat + fi * ROWF, ROWB, &bars[set]);
+  __device__ void issue(int bb) {   // whole warp 0; indices of batch bb are in fi / yi
+    const int set = bb % NS;
+    const int cnt = min(STAGES, ne - bb * STAGES);
+    if (lane == 0) mbar_expect_tx(&full[set], cnt * ROWB);
+    if (lane < cnt) bulk_load(sm.xs + (set * STAGES + lane) * ROWF, a.feat + fi * ROWF, ROWB, &full[set]);
     if (WITH_Y) {
 #pragma unroll
       for (int i0 = 0; i0 < STAGES * S::DY; i0 += 32) {
@@ -155,103 +201,134 @@ struct EdgeRing {
         if (i < cnt * S::DY) cp_async_4(sm.ys + set * STAGES * S::DY + i, a.y + yrow * S::DY + (i - ed * S::DY));
       }
     }
-    cp_async_arrive(&bars[set]);
+    cp_async_arrive(&full[set]);
   }
   __device__ void prologue() {
     if (warp != 0) return;
-    for (int64_t bb = 0; bb < NS - 1 && bb < nb; ++bb) {
+    for (int bb = 0; bb < LEAD && bb < nb; ++bb) {
       load_idx(bb);
       issue(bb);
     }
-    if (NS - 1 < nb) load_idx(NS - 1);
+    if (LEAD < nb) load_idx(LEAD);
   }
-  // start of iteration b (every warp has left batch b - 1, whose set is refilled now); returns false on a timeout
-  __device__ bool begin(int64_t b) {
+  // start of iteration b; returns false on a timeout
+  __device__ bool begin(int b) {
     if (warp == 0) {
-      const int64_t bb = b + NS - 1;
-      if (bb < nb) issue(bb);
+      const int bb = b + LEAD;
+      if (bb < nb) {
+        if (!SYNCED && bb >= NS) {   // the set's previous batch must have been released by every warp
+          int ok = (lane == 0) ? (int)mbar_wait(&empty[bb % NS], (uint32_t)(((bb / NS) - 1) & 1)) : 0;
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          __syncwarp();
+          if (!ok) return false;
+        }
+        issue(bb);
+      }
       if (bb + 1 < nb) load_idx(bb + 1);
     }
-    return mbar_wait(&bars[b % NS], (uint32_t)((b / NS) & 1));
+    return mbar_wait(&full[b % NS], (uint32_t)((b / NS) & 1));
+  }
+  __device__ void release(int b) {   // !SYNCED: this warp is done with batch b
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[b % NS]);
   }
   // after a timeout: give copies that may still be in flight a bounded chance to land before the CTA retires
-  __device__ void drain(int64_t b) {
+  __device__ void drain(int b) {
     asm volatile("cp.async.wait_all;" ::: "memory");
-    for (int64_t bb = b; bb < nb && bb < b + NS - 1; ++bb) mbar_wait(&bars[bb % NS], (uint32_t)((bb / NS) & 1));
+    for (int bb = b; bb < nb && bb < b + LEAD; ++bb) mbar_wait(&full[bb % NS], (uint32_t)((bb / NS) & 1));
   }
 };
 
+template <class S, int CPL, int CG>
+__device__ __forceinline__ const float4* role_scales(const Smem<S, CPL, CG>& sm, int role) {
+  return reinterpret_cast<const float4*>(sm.ssc + (role == 0 ? S::OT0 : role == 1 ? S::OT1 : role == 2 ? S::OT2 : S::OT3));
+}
+
 // ---- spec kernel: gather + outer product + per-node CG + segment sum ---------------------------------
-// Warp (cq, role): channels [32 cq, 32 cq + 32), one per lane; role selects the half of the (m_y, m_feat)
-// cells whose accumulators Q[cell] = sum_e y_e[m_y] x_e[m_feat] the warp keeps in registers.  When the
-// last edge of a node has been added the warp turns its Q into its share of the rows,
-// S[d, r] = sum_t scale[t] Q[cell(t)], stores them and clears Q.
-template <class S, int CQ>
-__global__ void __launch_bounds__(64 * CQ, 4 / CQ) tp_segsum_spec_kernel(FusedArgs a) {
-  using SM = Smem<S, CQ>;
-  constexpr int C = SM::C, ROWF = SM::ROWF, NT = 64 * CQ, NS = SM::NS;
+// Warp (cg, role): channels [32 CPL cg, 32 CPL (cg + 1)), CPL per lane; role selects the quarter of the
+// (m_y, m_feat) cells whose accumulators Q[cell] = sum_e y_e[m_y] x_e[m_feat] the warp keeps in
+// registers.  When the last edge of a node has been added the warp turns its Q into its share of the
+// rows, S[d, r] = sum_t scale[t] Q[cell(t)], stores them and clears Q.  Warps never wait for each other.
+template <class S, int CPL, int CG>
+__global__ void __launch_bounds__(128 * CG, CG == 1 ? 3 : 1) tp_segsum_spec_kernel(FusedArgs a) {
+  using SM = Smem<S, CPL, CG>;
+  constexpr int C = SM::C, ROWF = SM::ROWF, NT = SM::NT, NS = SM::NS;
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  __shared__ uint64_t bars[NS];
+  __shared__ uint64_t full[NS], empty[NS];
   SM sm(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int role = warp & 1, ch = (warp >> 1) * 32 + lane;
-  const float4* sc = reinterpret_cast<const float4*>(sm.ssc + (role ? S::OT1 : 0));
+  const int role = warp & 3, ch = ((warp >> 2) * 32 + lane) * CPL;
+  const float4* sc = role_scales(sm, role);
 
-  for (int t = tid; t < S::OT2; t += NT) sm.ssc[t] = __ldg(a.scale_o + t);
-  if (tid == 0) {
-    for (int i = 0; i < NS; ++i) mbar_init(&bars[i], 1 + 32);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
+  for (int t = tid; t < S::OT4; t += NT) sm.ssc[t] = __ldg(a.scale_o + t);
+  using Ring = EdgeRing<S, CPL, CG, true, false>;
+  if (tid == 0) Ring::init(full, empty);
   cta_sync();
 
   const int64_t d0 = (int64_t)blockIdx.x * a.nodes_per_cta;
-  const int64_t d1 = min(d0 + a.nodes_per_cta, a.n_out);
+  const int nd = (int)min((int64_t)a.nodes_per_cta, a.n_out - d0);
   const int64_t e0 = a.ptr ? __ldg(a.ptr + d0) : d0;
-  const int64_t e1 = a.ptr ? __ldg(a.ptr + d1) : d1;
-  EdgeRing<S, CQ, true> ring(a, sm, bars, e0, e1, warp, lane);
+  const int ne = (int)((a.ptr ? __ldg(a.ptr + d0 + nd) : d0 + nd) - e0);
+  Ring ring(a, sm, full, empty, e0, ne, warp, lane);
   ring.prologue();
 
-  float q[S::MAXCELL];
+  float q[S::MAXCELL][CPL];
 #pragma unroll
-  for (int i = 0; i < S::MAXCELL; ++i) q[i] = 0.f;
+  for (int i = 0; i < S::MAXCELL; ++i)
+#pragma unroll
+    for (int k = 0; k < CPL; ++k) q[i][k] = 0.f;
 
-  int64_t d_cur = d0;
-  int64_t boundary = a.ptr ? __ldg(a.ptr + d_cur + 1) : d_cur + 1;
-  auto flush = [&]() {   // a node without edges flushes a zero Q, i.e. zero rows
-    float* o = a.out + d_cur * S::R * C + ch;
-    if (role == 0) S::template node_r0<C>(q, sc, o);
-    else S::template node_r1<C>(q, sc, o);
+  // nodes and edges are counted from the CTA's first (d0, e0) in 32 bits to save registers
+  const int64_t* ptr = a.ptr ? a.ptr + d0 : nullptr;
+  float* o = a.out + d0 * S::R * C + ch;
+  int d_cur = 0;
+  int boundary = ptr ? (int)(__ldg(ptr + 1) - e0) : 1;   // first edge of the next node
+  auto flush = [&]() __attribute__((always_inline)) {   // a node without edges flushes a zero Q, i.e. zero rows
+    if (role == 0) S::template node_r0<CPL, C>(q, sc, o);
+    else if (role == 1) S::template node_r1<CPL, C>(q, sc, o);
+    else if (role == 2) S::template node_r2<CPL, C>(q, sc, o);
+    else S::template node_r3<CPL, C>(q, sc, o);
 #pragma unroll
-    for (int i = 0; i < S::MAXCELL; ++i) q[i] = 0.f;
+    for (int i = 0; i < S::MAXCELL; ++i)
+#pragma unroll
+      for (int k = 0; k < CPL; ++k) q[i][k] = 0.f;
     ++d_cur;
-    if (d_cur < d1) boundary = a.ptr ? __ldg(a.ptr + d_cur + 1) : d_cur + 1;
+    o += S::R * C;
+    if (d_cur < nd) boundary = ptr ? (int)(__ldg(ptr + d_cur + 1) - e0) : d_cur + 1;
   };
 
-  for (int64_t b = 0; b < ring.nb; ++b) {
+  for (int b = 0; b < ring.nb; ++b) {
     if (!ring.begin(b)) {
-      if (tid == 0) atomicExch(a.status, 1);
+      if (lane == 0) atomicExch(a.status, 1);
       ring.drain(b);
       return;
     }
-    const int set = (int)(b % NS);
-    const int64_t eb = e0 + b * STAGES;
-    const int cnt = (int)min((int64_t)STAGES, e1 - eb);
+    const int set = b % NS;
+    const int cnt = min(STAGES, ne - b * STAGES);
     for (int s = 0; s < cnt; ++s) {
-      const int64_t e = eb + s;
+      const int e = b * STAGES + s;
       while (e >= boundary) flush();
-      float x[S::DF], yv[S::DY];
+      float yv[S::DY];
       const float* xr = sm.xs + (set * STAGES + s) * ROWF + ch;
       const float* yr = sm.ys + (set * STAGES + s) * S::DY;
+      if constexpr (S::DY % 4 == 0) {
 #pragma unroll
-      for (int m = 0; m < S::DF; ++m) x[m] = xr[m * C];
+        for (int k = 0; k < S::DY; k += 4) {
+          const float4 v = *reinterpret_cast<const float4*>(yr + k);
+          yv[k] = v.x; yv[k + 1] = v.y; yv[k + 2] = v.z; yv[k + 3] = v.w;
+        }
+      } else {
 #pragma unroll
-      for (int k = 0; k < S::DY; ++k) yv[k] = yr[k];
-      if (role == 0) S::outer_r0(q, x, yv);
-      else S::outer_r1(q, x, yv);
+        for (int k = 0; k < S::DY; ++k) yv[k] = yr[k];
+      }
+      if (role == 0) S::template outer_r0<CPL, C>(q, xr, yv);
+      else if (role == 1) S::template outer_r1<CPL, C>(q, xr, yv);
+      else if (role == 2) S::template outer_r2<CPL, C>(q, xr, yv);
+      else S::template outer_r3<CPL, C>(q, xr, yv);
     }
-    cta_sync();   // everybody is done with this set before it is refilled
+    ring.release(b);
   }
-  while (d_cur < d1) flush();
+  while (d_cur < nd) flush();
 }
 
 // Sum each of the N per-lane values over the 32 lanes and store the N totals.  For N = 16 the
@@ -285,65 +362,70 @@ __device__ __forceinline__ void warp_reduce_to_smem(float (&v)[N], float* dst, i
 // ---- spec kernel: adjoint w.r.t. the channel-less operand ----------------------------------------
 // gy_e[k] = sum_{cells (k, m)} sum_c x_e[m, c] H_d[cell, c]  with  H_d[cell] = sum_{t in cell} scale[t] G_d[row(t)]
 // built once per node in registers (same warp roles as above), then one dense dot product per edge.
-template <class S, int CQ>
-__global__ void __launch_bounds__(64 * CQ, 4 / CQ) tp_inner_spec_kernel(FusedArgs a) {
-  using SM = Smem<S, CQ>;
-  constexpr int C = SM::C, ROWF = SM::ROWF, NT = 64 * CQ, NWARP = SM::NWARP, NS = SM::NS;
+template <class S, int CPL, int CG>
+__global__ void __launch_bounds__(128 * CG, CG == 1 ? 3 : 1) tp_inner_spec_kernel(FusedArgs a) {
+  using SM = Smem<S, CPL, CG>;
+  constexpr int C = SM::C, ROWF = SM::ROWF, NT = SM::NT, NWARP = SM::NWARP, NS = SM::NS;
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  __shared__ uint64_t bars[NS];
+  __shared__ uint64_t full[NS], empty[NS];
   SM sm(smem_raw);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int role = warp & 1, ch = (warp >> 1) * 32 + lane;
-  const float4* sc = reinterpret_cast<const float4*>(sm.ssc + (role ? S::OT1 : 0));
-  for (int t = tid; t < S::OT2; t += NT) sm.ssc[t] = __ldg(a.scale_o + t);
-  if (tid == 0) {
-    for (int i = 0; i < NS; ++i) mbar_init(&bars[i], 1 + 32);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
+  const int role = warp & 3, ch = ((warp >> 2) * 32 + lane) * CPL;
+  const float4* sc = role_scales(sm, role);
+  for (int t = tid; t < S::OT4; t += NT) sm.ssc[t] = __ldg(a.scale_o + t);
+  using Ring = EdgeRing<S, CPL, CG, false, true>;
+  if (tid == 0) Ring::init(full, empty);
   cta_sync();
 
   const int64_t d0 = (int64_t)blockIdx.x * a.nodes_per_cta;
-  const int64_t d1 = min(d0 + a.nodes_per_cta, a.n_out);
-  const int64_t e0 = __ldg(a.ptr + d0), e1 = __ldg(a.ptr + d1);
-  EdgeRing<S, CQ, false> ring(a, sm, bars, e0, e1, warp, lane);
+  const int nd = (int)min((int64_t)a.nodes_per_cta, a.n_out - d0);
+  const int64_t* ptr = a.ptr + d0;
+  const int64_t e0 = __ldg(ptr);
+  const int ne = (int)(__ldg(ptr + nd) - e0);
+  Ring ring(a, sm, full, empty, e0, ne, warp, lane);
   ring.prologue();
 
-  float h[S::MAXCELL];
+  float h[S::MAXCELL][CPL];
 #pragma unroll
-  for (int i = 0; i < S::MAXCELL; ++i) h[i] = 0.f;
-  int64_t d_cur = d0 - 1;
-  int64_t boundary = e0;   // forces H to be built for the first node that has an edge
-  auto next_node = [&]() {
+  for (int i = 0; i < S::MAXCELL; ++i)
+#pragma unroll
+    for (int k = 0; k < CPL; ++k) h[i][k] = 0.f;
+  // nodes and edges are counted from the CTA's first (d0, e0) in 32 bits to save registers
+  const float* gp = a.g + (d0 - 1) * S::R * C + ch;
+  int d_cur = -1;
+  int boundary = 0;   // forces H to be built for the first node that has an edge
+  auto next_node = [&]() __attribute__((always_inline)) {
     ++d_cur;
-    boundary = __ldg(a.ptr + d_cur + 1);
-    if (boundary > __ldg(a.ptr + d_cur)) {
-      const float* gp = a.g + d_cur * S::R * C + ch;
-      if (role == 0) S::template hbuild_r0<C>(h, sc, gp);
-      else S::template hbuild_r1<C>(h, sc, gp);
+    gp += S::R * C;
+    const int begin = boundary;
+    boundary = (int)(__ldg(ptr + d_cur + 1) - e0);
+    if (boundary > begin) {
+      if (role == 0) S::template hbuild_r0<CPL, C>(h, sc, gp);
+      else if (role == 1) S::template hbuild_r1<CPL, C>(h, sc, gp);
+      else if (role == 2) S::template hbuild_r2<CPL, C>(h, sc, gp);
+      else S::template hbuild_r3<CPL, C>(h, sc, gp);
     }
   };
 
-  for (int64_t b = 0; b < ring.nb; ++b) {
+  for (int b = 0; b < ring.nb; ++b) {
     if (!ring.begin(b)) {
-      if (tid == 0) atomicExch(a.status, 1);
+      if (lane == 0) atomicExch(a.status, 1);
       ring.drain(b);
       return;
     }
-    const int set = (int)(b % NS), rset = (int)(b & 1);
-    const int64_t eb = e0 + b * STAGES;
-    const int cnt = (int)min((int64_t)STAGES, e1 - eb);
+    const int set = b % NS, rset = b & 1;
+    const int cnt = min(STAGES, ne - b * STAGES);
     for (int s = 0; s < cnt; ++s) {
-      const int64_t e = eb + s;
+      const int e = b * STAGES + s;
       while (e >= boundary) next_node();
-      float x[S::DF];
       const float* xr = sm.xs + (set * STAGES + s) * ROWF + ch;
-#pragma unroll
-      for (int m = 0; m < S::DF; ++m) x[m] = xr[m * C];
       float ay[S::DY];
 #pragma unroll
       for (int k = 0; k < S::DY; ++k) ay[k] = 0.f;
-      if (role == 0) S::dot_r0(ay, x, h);
-      else S::dot_r1(ay, x, h);
+      if (role == 0) S::template dot_r0<CPL, C>(ay, xr, h);
+      else if (role == 1) S::template dot_r1<CPL, C>(ay, xr, h);
+      else if (role == 2) S::template dot_r2<CPL, C>(ay, xr, h);
+      else S::template dot_r3<CPL, C>(ay, xr, h);
       float* rd = sm.red + ((rset * STAGES + s) * NWARP + warp) * S::DY;
       warp_reduce_to_smem<S::DY>(ay, rd, lane);
     }
@@ -355,7 +437,7 @@ __global__ void __launch_bounds__(64 * CQ, 4 / CQ) tp_inner_spec_kernel(FusedArg
       float v = rd[0];
 #pragma unroll
       for (int w = 1; w < NWARP; ++w) v += rd[w * S::DY];
-      const int64_t e = eb + s;
+      const int64_t e = e0 + b * STAGES + s;
       a.out[(a.yidx ? __ldg(a.yidx + e) : e) * S::DY + k] = v;
     }
   }
@@ -412,10 +494,10 @@ __global__ void __launch_bounds__(128) tp_inner_generic_kernel(FusedArgs a) {
 }
 
 // ---- dispatch ------------------------------------------------------------------------------------
-template <class S, int CQ>
+template <class S, int CPL, int CG>
 int launch_spec(bool inner, const FusedArgs& a, cudaStream_t s) {
-  constexpr size_t bytes = Smem<S, CQ>::bytes();
-  auto kern = inner ? tp_inner_spec_kernel<S, CQ> : tp_segsum_spec_kernel<S, CQ>;
+  constexpr size_t bytes = Smem<S, CPL, CG>::bytes();
+  auto kern = inner ? tp_inner_spec_kernel<S, CPL, CG> : tp_segsum_spec_kernel<S, CPL, CG>;
   static bool configured[2] = {false, false};
   if (!configured[inner]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
@@ -423,22 +505,22 @@ int launch_spec(bool inner, const FusedArgs& a, cudaStream_t s) {
     configured[inner] = true;
   }
   const unsigned grid = (unsigned)ceil_div(a.n_out, a.nodes_per_cta);
-  kern<<<grid, 64 * CQ, bytes, s>>>(a);
+  kern<<<grid, 128 * CG, bytes, s>>>(a);
   return check_launch(inner ? "tp_inner_spec_kernel" : "tp_segsum_spec_kernel");
 }
 
 template <class S>
 bool try_spec(uint64_t key, bool inner, const FusedArgs& a, cudaStream_t s, int& rc) {
   if (key != S::KEY || a.T != S::T || a.R != S::R || a.DF != S::DF || a.DY != S::DY) return false;
-  if (a.C == 128) { rc = launch_spec<S, 4>(inner, a, s); return true; }
-  if (a.C == 64) { rc = launch_spec<S, 2>(inner, a, s); return true; }
-  if (a.C == 32) { rc = launch_spec<S, 1>(inner, a, s); return true; }
+  if (a.C == 128) { rc = launch_spec<S, 2, 2>(inner, a, s); return true; }
+  if (a.C == 64) { rc = launch_spec<S, 2, 1>(inner, a, s); return true; }
+  if (a.C == 32) { rc = launch_spec<S, 1, 1>(inner, a, s); return true; }
   return false;
 }
 
 int run(bool inner, const eqt_tp_table* tab, FusedArgs a, cudaStream_t s) {
   if (a.n_out == 0 || (inner && a.n_edges == 0)) return EQT_OK;
-  if ((reinterpret_cast<uintptr_t>(a.feat) & 15u) == 0 && a.status && a.scale_o && (!inner || a.ptr)) {
+  if ((reinterpret_cast<uintptr_t>(a.feat) & 15u) == 0 && a.status && a.scale_o && (!inner || a.ptr) && a.n_edges < 0x7fffffffll) {
     // nodes per CTA: keep every SM busy with several CTAs but amortise the pipeline prologue
     int64_t per = std::max<int64_t>(1, a.n_out / (148 * 16));
     const int64_t avg_deg = std::max<int64_t>(1, a.n_edges / std::max<int64_t>(1, a.n_out));
