@@ -48,11 +48,6 @@ class TpTableStruct(C.Structure):
                 ("structure_key", C.c_uint64), ("scale_o", C.c_void_p)]
 
 
-class CgTcTableStruct(C.Structure):
-    _fields_ = [("u_row", C.c_void_p), ("u_m", C.c_void_p), ("u_scale", C.c_void_p), ("u_my", C.c_void_p),
-                ("num_entries", C.c_int32), ("num_rows", C.c_int32), ("d_feat", C.c_int32), ("d_y", C.c_int32)]
-
-
 class MixBlockStruct(C.Structure):
     _fields_ = [("in_row0", C.c_int32), ("out_row0", C.c_int32), ("dim", C.c_int32), ("paths", C.c_int32),
                 ("w_offset", C.c_int64)]
@@ -83,9 +78,6 @@ SIGNATURES = {
     "eqt_wgrad_tc_static_capacity": (C.c_int64, []),
     "eqt_pack_weights": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_int32,
                                    C.c_void_p, C.c_void_p, C.c_void_p]),
-    "eqt_tp_cg_segment_sum_tc": (C.c_int, [C.POINTER(CgTcTableStruct), C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p,
-                                           C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p,
-                                           C.c_void_p]),
     "eqt_last_error": (C.c_char_p, []),
     "eqt_version": (C.c_int, []),
     "eqt_launch_count": (C.c_int64, []),

@@ -54,35 +54,6 @@ class TpTable:
         self.struct = _lib.TpTableStruct(self.scale.data_ptr(), self.m_feat.data_ptr(), self.m_y.data_ptr(),
                                          self.row_ptr.data_ptr(), self.num_entries, self.num_rows, d_feat, d_y, self.key,
                                          self.scale_o.data_ptr())
-        self.tc_struct = self._merged(s, device)
-
-    def _merged(self, s, device):
-        """Table for the tensor-core CG step: entries with the same (row, feature component) merged.
-
-        Returns ``None`` when the structure does not fit that kernel (more than two harmonics terms per
-        coefficient, more than 128 rows, 16 feature components or 512 coefficients).
-        """
-        if s.num_rows > 128 or s.d_feat > 16 or s.d_y > 16 or len(s.mf) == 0:
-            return None
-        slot = s.row * s.d_feat + s.mf
-        uniq, inv, counts = np.unique(slot, return_inverse=True, return_counts=True)
-        if counts.max() > 2 or len(uniq) > 512:
-            return None
-        scale = self.scale.cpu().numpy()
-        u_scale = np.zeros((len(uniq), 2), dtype=np.float32)
-        u_my = np.zeros((len(uniq), 2), dtype=np.uint8)
-        fill = np.zeros(len(uniq), dtype=np.int64)
-        for t in range(len(slot)):
-            u = inv[t]
-            u_scale[u, fill[u]] = scale[t]
-            u_my[u, fill[u]] = s.my[t]
-            fill[u] += 1
-        self.u_row = torch.from_numpy((uniq // s.d_feat).astype(np.uint8)).to(device)
-        self.u_m = torch.from_numpy((uniq % s.d_feat).astype(np.uint8)).to(device)
-        self.u_scale = torch.from_numpy(u_scale).to(device)
-        self.u_my = torch.from_numpy(u_my).to(device)
-        return _lib.CgTcTableStruct(self.u_row.data_ptr(), self.u_m.data_ptr(), self.u_scale.data_ptr(),
-                                    self.u_my.data_ptr(), len(uniq), s.num_rows, s.d_feat, s.d_y)
 
 
 def _f32(t: Tensor, what: str) -> Tensor:
@@ -91,25 +62,9 @@ def _f32(t: Tensor, what: str) -> Tensor:
     return t.contiguous()
 
 
-#: route ``cg_segment_sum`` through the tcgen05 kernel when the table and the shapes allow it.  Off by
-#: default: at l_max = 3, C = 64 the dense per-edge coefficient matrix costs 17x the flops of the sparse
-#: loop and the kernel measured 8.2 ms against 4.0 ms for the CUDA-core kernel (2M edges, B200).
-TENSOR_CORE_CG = False
-
-
-def tensor_core_cg_supported(table: TpTable, feat: Tensor, seg_ptr: Optional[Tensor], n_edges: int) -> bool:
-    c = feat.shape[2]
-    return (table.tc_struct is not None and seg_ptr is not None and c % 32 == 0 and c <= 128 and n_edges > 0
-            and feat.data_ptr() % 16 == 0)
-
-
 def cg_segment_sum(table: TpTable, feat: Tensor, y: Tensor, feat_index: Optional[Tensor], y_index: Optional[Tensor],
-                   seg_ptr: Optional[Tensor], num_out: int, tensor_core: Optional[bool] = None) -> Tensor:
-    """``out[d, r, :] = sum_{e in seg[d]} sum_{t in r} scale[t] y[y_index[e], m_y[t]] feat[feat_index[e], m_feat[t], :]``.
-
-    ``tensor_core``: ``True`` forces the tcgen05 kernel (error if unsupported), ``False`` the CUDA-core
-    kernels, ``None`` picks the tcgen05 kernel when supported and ``TENSOR_CORE_CG`` is set.
-    """
+                   seg_ptr: Optional[Tensor], num_out: int) -> Tensor:
+    """``out[d, r, :] = sum_{e in seg[d]} sum_{t in r} scale[t] y[y_index[e], m_y[t]] feat[feat_index[e], m_feat[t], :]``."""
     dev = _lib.require_cuda(feat, y, feat_index, y_index, seg_ptr)
     feat, y = _f32(feat, "feat"), _f32(y, "y")
     assert feat.ndim == 3 and feat.shape[1] == table.d_feat and y.shape[-1] == table.d_y
@@ -118,17 +73,6 @@ def cg_segment_sum(table: TpTable, feat: Tensor, y: Tensor, feat_index: Optional
     if seg_ptr is None:
         num_out = n_edges
     out = torch.empty(num_out, table.num_rows, c, dtype=torch.float32, device=dev)
-    if tensor_core is None:
-        tensor_core = TENSOR_CORE_CG and tensor_core_cg_supported(table, feat, seg_ptr, n_edges)
-    if tensor_core:
-        if table.tc_struct is None or seg_ptr is None:
-            raise _lib.EqtError("this table / call has no tensor-core form")
-        with torch.cuda.device(dev):
-            _lib.check(_lib.lib().eqt_tp_cg_segment_sum_tc(
-                C.byref(table.tc_struct), feat.data_ptr(), feat.shape[0], _lib.ptr(feat_index), y.data_ptr(),
-                _lib.ptr(y_index), seg_ptr.data_ptr(), out.data_ptr(), num_out, c, status_flag(dev).data_ptr(),
-                _lib.stream_ptr(dev)), "eqt_tp_cg_segment_sum_tc")
-        return out
     with torch.cuda.device(dev):
         _lib.check(_lib.lib().eqt_tp_cg_segment_sum(
             C.byref(table.struct), feat.data_ptr(), _lib.ptr(feat_index), y.data_ptr(), _lib.ptr(y_index),

@@ -167,32 +167,6 @@ int eqt_tp_cg_segment_sum(const eqt_tp_table* table, const float* feat, const in
                           int64_t num_out, int64_t num_edges, int32_t channels, int32_t* status, void* stream);
 
 /*
- * Tensor-core form of eqt_tp_cg_segment_sum (same result, float32 in and out, 3xTF32 arithmetic): per
- * node one tcgen05 GEMM  S[d] = [B_e1 | B_e2 | ...] * [X_e1; X_e2; ...]  over the node's edges, with
- * B_e[r, m] = sum of scale * y over the table entries of intermediate row r and feature component m.
- * The table is passed with those entries merged: entry u contributes
- *   (u_scale[2u] * y[u_my[2u]] + u_scale[2u+1] * y[u_my[2u+1]])  at (u_row[u], u_m[u])
- * (a missing second term has scale 0).  Needs num_rows <= 128, d_feat <= 16, num_entries <= 512,
- * channels in {32, 64, 96, 128}, seg_ptr != NULL; feat has feat_rows rows.  `status` is set to 4 if a
- * bounded wait expired.  replaces: the same reference chain as eqt_tp_cg_segment_sum.
- */
-typedef struct eqt_cg_tc_table {
-  const uint8_t* u_row;     /* (U,) device */
-  const uint8_t* u_m;       /* (U,) device */
-  const float* u_scale;     /* (U, 2) device */
-  const uint8_t* u_my;      /* (U, 2) device */
-  int32_t num_entries;      /* U */
-  int32_t num_rows;         /* R */
-  int32_t d_feat;
-  int32_t d_y;
-} eqt_cg_tc_table;
-
-int eqt_tp_cg_segment_sum_tc(const eqt_cg_tc_table* table, const float* feat, int64_t feat_rows,
-                             const int64_t* feat_index, const float* y, const int64_t* y_index,
-                             const int64_t* seg_ptr, float* out, int64_t num_out, int32_t channels,
-                             int32_t* status, void* stream);
-
-/*
  * Adjoint of the CG step with respect to the channel-less operand (float32):
  *   grad_y[y_index[e] | e, k] = sum_{t: m_y[t] = k} scale[t] * sum_c feat[feat_index[e] | e, m_feat[t], c] * g[node(e), row(t), c]
  * g (num_nodes, R, channels) holds the gradient with respect to the intermediate, already summed
