@@ -325,10 +325,20 @@ def main():
                        "algorithmic_GBps": round(gbs, 1), "frac_of_hbm_peak": round(gbs / pk["hbm_gbs"], 4)}
     top = next(iter(table)) if table else None
     roofline = None
+    # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures of the 499,040-edge profiling
+    # workload (profiles/), scaled to this launch by its edge count (same degree, so nodes scale alike).  The node
+    # features of the profiling workload fit L2 and those of the full workload do not, so for the gathering
+    # kernels the scaled figure is a lower bound.
+    ncu_dram_bytes_cfg5q = {
+        "cg_segment_sum[fwd]": 201.3e6 + 582.9e6, "cg_segment_sum[grad_x]": 192.0e6 + 579.6e6,
+        "cg_inner[grad_y]": 796.2e6 + 34.5e6, "channel_mix[fwd]": 723.0e6, "channel_mix[grad_x]": 723.0e6,
+    }
     if top:
         roofline = {"kernel": top, "bound": "hbm", "achieved": table[top]["algorithmic_GBps"], "peak": pk["hbm_gbs"],
                     "unit": "GB/s", "frac": table[top]["frac_of_hbm_peak"], "peak_source": pk["source"],
-                    "algorithmic_bytes_per_launch": algorithmic.get(top), "traffic": None}
+                    "algorithmic_bytes_per_launch": algorithmic.get(top),
+                    "traffic": (int(ncu_dram_bytes_cfg5q[top] * n_edges_local / 499040)
+                                if top in ncu_dram_bytes_cfg5q else None)}
 
     result = {
         "metric": METRIC, "value": value, "unit": "edges/s", "n_gpus": world, "steps": args.steps,
