@@ -198,14 +198,20 @@ def _emit_outer_role(s: Structure, plan: OuterPlan, w: int) -> List[str]:
                 touched.add(cell)
                 out.append(f"    EQT_MUL(h[{cell}], gr, {term});")
     out.append("  }")
-    # adjoint, per edge: ay[m_y] += <x[m_feat], h[cell]> over the lane's channels
+    # adjoint, per edge: ay[m_y] = sum over the role's cells of <x[m_feat], h[cell]> over the lane's channels
+    kys = set(int(k) for k, _ in cells)
     out.append("  template <int CPL, int C> __device__ __forceinline__ static void "
                f"dot_r{w}(float (&ay)[DY], const float* xr, const float (&h)[MAXCELL][CPL]) {{")
     out.append("    float x[CPL];")
+    first = set()
+    for k in range(s.d_y):
+        if k not in kys:
+            out.append(f"    ay[{k}] = 0.f;")
     for m in sorted(by_m):
         out.append(f"    EQT_LDX(x, xr + {m} * C);")
         for i, k in by_m[m]:
-            out.append(f"    EQT_DOT(ay[{k}], x, h[{i}]);")
+            out.append(f"    EQT_DOT(ay[{k}], x, h[{i}]);" if k in first else f"    EQT_DOT0(ay[{k}], x, h[{i}]);")
+            first.add(k)
     out.append("  }")
     return out
 

@@ -46,6 +46,7 @@ template <int CPL> __device__ __forceinline__ void st_lane(float* p, const float
 #define EQT_MUL(ACC, A, S) do { _Pragma("unroll") for (int k_ = 0; k_ < CPL; ++k_) (ACC)[k_] = (A)[k_] * (S); } while (0)
 #define EQT_ZERO(V) do { _Pragma("unroll") for (int k_ = 0; k_ < CPL; ++k_) (V)[k_] = 0.f; } while (0)
 #define EQT_DOT(ACC, X, H) do { _Pragma("unroll") for (int k_ = 0; k_ < CPL; ++k_) (ACC) = fmaf((X)[k_], (H)[k_], (ACC)); } while (0)
+#define EQT_DOT0(ACC, X, H) do { (ACC) = (X)[0] * (H)[0]; _Pragma("unroll") for (int k_ = 1; k_ < CPL; ++k_) (ACC) = fmaf((X)[k_], (H)[k_], (ACC)); } while (0)
 #include "generated/tp_specs.inc"
 #undef EQT_LDX
 #undef EQT_LDG
@@ -54,6 +55,7 @@ template <int CPL> __device__ __forceinline__ void st_lane(float* p, const float
 #undef EQT_MUL
 #undef EQT_ZERO
 #undef EQT_DOT
+#undef EQT_DOT0
 }  // namespace specs
 
 namespace {
@@ -419,9 +421,7 @@ __global__ void __launch_bounds__(128 * CG, CG == 1 ? 3 : 1) tp_inner_spec_kerne
       const int e = b * STAGES + s;
       while (e >= boundary) next_node();
       const float* xr = sm.xs + (set * STAGES + s) * ROWF + ch;
-      float ay[S::DY];
-#pragma unroll
-      for (int k = 0; k < S::DY; ++k) ay[k] = 0.f;
+      float ay[S::DY];   // fully written by dot_r*
       if (role == 0) S::template dot_r0<CPL, C>(ay, xr, h);
       else if (role == 1) S::template dot_r1<CPL, C>(ay, xr, h);
       else if (role == 2) S::template dot_r2<CPL, C>(ay, xr, h);
