@@ -184,6 +184,7 @@ def main():
     ap.add_argument("--workload", default="cfg5", choices=["cfg5", "cfg2", "cfg5q"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="time the eager step only (no CUDA-graph replay)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -204,7 +205,8 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     if args.workload == "cfg2" and world > 1:
         raise SystemExit("cfg2 is the single-GPU microbenchmark")
 
@@ -253,12 +255,15 @@ def main():
     if flush is None:
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0.record()
+        host0 = time.perf_counter()
         for _ in range(args.steps):
             step(x_dev, vec_dev)
+        host_enqueue_ms = (time.perf_counter() - host0) * 1e3   # time the host needed to enqueue the steps
         t1.record()
         barrier()
         elapsed_ms = t0.elapsed_time(t1)
     else:
+        host_enqueue_ms = None
         pairs = []
         for _ in range(args.steps):
             flush.zero_()
@@ -272,8 +277,44 @@ def main():
     launches = _lib.launch_count() - launches0
     kernels = _profile.collect()
     _profile.enable(False)
-    clocks = sampler.stop()
     check_status()
+    graph_error = None
+
+    # ---- the same step replayed as a CUDA graph (removes the Python launch overhead, which bounds the step at
+    # small per-GPU sizes); two graphs on two sets of input buffers so that the end-to-end loop can overlap the
+    # next step's copy.  The eager numbers above stay in the line as `eager_ms_per_step`.
+    eager_ms, graphed = elapsed_ms, None
+    bufs = [(x_dev, vec_dev),
+            (torch.empty_like(x_dev).requires_grad_(True), torch.empty_like(vec_dev).requires_grad_(True))]
+    with torch.no_grad():
+        bufs[1][0].copy_(x_dev)
+        bufs[1][1].copy_(vec_dev)
+    if flush is None and not args.no_graph:
+        try:
+            from equitorch_b200.utils.cuda_graph import GraphedStep
+            graphed = [GraphedStep(lambda xb=xb, vb=vb: step(xb, vb), dev, warmup=2) for xb, vb in bufs]
+        except Exception as exc:  # noqa: BLE001 - any capture failure falls back to the eager loop
+            graphed, graph_error = None, f"{type(exc).__name__}: {exc}"[:300]
+            torch.cuda.synchronize(dev)
+        if world > 1:                       # replay on every rank or on none
+            flag = torch.tensor([1 if graphed is not None else 0], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            if int(flag.item()) == 0:
+                graphed = None
+    if graphed is not None:
+        for _ in range(3):
+            graphed[0].replay()
+        check_status()
+        barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for i in range(args.steps):
+            graphed[i % 2].replay()
+        t1.record()
+        barrier()
+        elapsed_ms = t0.elapsed_time(t1)
+        check_status()
+    clocks = sampler.stop()
 
     # ---- end-to-end timing: host buffers in, result out, every step ----------------------------
     # Every step copies its own inputs from pinned host memory and reads its result back.  The copy of step
@@ -281,13 +322,12 @@ def main():
     # loader would do it; all copies are inside the timed region.
     copy_stream = torch.cuda.Stream(dev)
     main_stream = torch.cuda.current_stream(dev)
-    bufs = [(torch.empty_like(x_dev, requires_grad=False), torch.empty_like(vec_dev, requires_grad=False)) for _ in range(2)]
     ready = [torch.cuda.Event() for _ in range(2)]
     consumed = [torch.cuda.Event() for _ in range(2)]
 
     def enqueue_inputs(i):
         slot = i % 2
-        with torch.cuda.stream(copy_stream):
+        with torch.cuda.stream(copy_stream), torch.no_grad():
             if i >= 2:
                 copy_stream.wait_event(consumed[slot])      # step i - 2 has finished with this buffer
             bufs[slot][0].copy_(x_host, non_blocking=True)
@@ -302,9 +342,10 @@ def main():
         if i + 1 < args.steps:
             enqueue_inputs(i + 1)
         main_stream.wait_event(ready[i % 2])
-        xd = bufs[i % 2][0].detach().requires_grad_(True)
-        vd = bufs[i % 2][1].detach().requires_grad_(True)
-        out, gx, gv, gw = step(xd, vd)
+        if graphed is not None:
+            out, gx, gv, gw = graphed[i % 2].replay()
+        else:
+            out, gx, gv, gw = step(*bufs[i % 2])
         consumed[i % 2].record(main_stream)
         loss_host.copy_((out * cot).sum().reshape(1), non_blocking=True)
         gw_host.copy_(gw, non_blocking=True)
@@ -314,10 +355,10 @@ def main():
     e2e_ms = e0_.elapsed_time(e1_)
     check_status()
 
-    times = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=dev)
+    times = torch.tensor([elapsed_ms, e2e_ms, eager_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    elapsed_ms, e2e_ms = (float(v) for v in times.tolist())
+    elapsed_ms, e2e_ms, eager_ms = (float(v) for v in times.tolist())
     steps = max(1, args.steps)
     value = n_edges_total * steps / (elapsed_ms * 1e-3)
     e2e_value = n_edges_total * steps / (e2e_ms * 1e-3)
@@ -377,13 +418,27 @@ def main():
                 else int(x_all.numel() * 4 + graph.edge_vec.numel() * 4),
                 "d2h_bytes_per_step": int(4 + gw_host.numel() * 4) * world},
         "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "kernels": table,
+        "host_enqueue_ms_per_step": (round(host_enqueue_ms / steps, 3) if host_enqueue_ms is not None else None),
+        "cuda_graph": graphed is not None, "cuda_graph_error": graph_error,
+        "eager_ms_per_step": round(eager_ms / steps, 4),
     }
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             result["cpu_baseline"] = cpu_baseline(graph, x_all, cot_all, weight)
-        print(json.dumps(result))
+        print(json.dumps(result), flush=True)
+    # Tear down in a fixed order: graphs that captured collectives first, then the process group.  Destroying the
+    # NCCL communicator while such graphs were alive left the ranks waiting at exit; after the final barrier every
+    # rank leaves through os._exit so that no finaliser can wait on a peer that has already gone.
+    graphed = None
+    import gc
+    gc.collect()
+    torch.cuda.synchronize(dev)
     if world > 1:
-        dist.destroy_process_group()
+        dist.barrier()
+        torch.cuda.synchronize(dev)
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -47,6 +47,7 @@ class MixPlan:
         self.rows = int(len(w))
         self.comps = n_out
         self.path_gather = torch.tensor(gather, dtype=torch.long, device=device)
+        self.paths_in_order = list(gather) == list(range(len(gather)))   # packed path p is weight path p
         self.regular = len(blocks) > 0 and comp == n_out
         self._struct_cache = {}
 
@@ -123,7 +124,7 @@ def wgrad_tc(s: Tensor, g: Tensor, plan: MixPlan, num_paths: int) -> Tensor:
         _lib.check(_lib.lib().eqt_wgrad_tc(s.data_ptr(), g.data_ptr(), packed.data_ptr(), scratch.data_ptr(),
                                            scratch.numel(), n, rows, plan.comps, cin, cout, blocks, len(blocks),
                                            status_flag(dev).data_ptr(), _lib.stream_ptr(dev)), "eqt_wgrad_tc")
-    if plan.path_gather.numel() == num_paths and bool((plan.path_gather == torch.arange(num_paths, device=dev)).all()):
+    if plan.paths_in_order and plan.path_gather.numel() == num_paths:
         return packed
     return torch.zeros(num_paths, cin, cout, dtype=torch.float32, device=dev).index_add_(0, plan.path_gather, packed)
 
