@@ -27,6 +27,8 @@
 // Every wait on an mbarrier is bounded; on expiry the kernel raises the status flag, stops
 // issuing work, frees its TMEM and returns.
 #include <algorithm>
+#include <cstdlib>
+#include <string>
 #include <vector>
 
 #include "tc_common.cuh"
@@ -55,7 +57,8 @@ struct MixLaunch {
   int num_jobs;
   int max_cols;         // largest N among the jobs: fixes the stage layout and the TMEM split
   int stages;
-  int tmem_cols;        // power of two >= 2 * max_cols
+  int tmem_cols;        // power of two >= 2 * max_cols (+ 64 per stage with a_in_tmem)
+  int a_in_tmem;        // split A operand lives in tensor memory instead of shared memory
   int* status;
 };
 
@@ -83,6 +86,15 @@ struct GemmJob {
   int64_t out_node_stride, out_m_stride;   // floats
 };
 
+// EQT_MIX_A=smem keeps the split A operand in shared memory (for comparisons); default: tensor memory
+bool mix_a_in_tmem() {
+  static const bool on = [] {
+    const char* v = std::getenv("EQT_MIX_A");
+    return !(v && std::string(v) == "smem");
+  }();
+  return on;
+}
+
 int launch_jobs(const GemmJob* jobs, int count, int64_t n, int* status, cudaStream_t st) {
   static bool configured = false;
   if (!configured) {
@@ -96,11 +108,20 @@ int launch_jobs(const GemmJob* jobs, int count, int64_t n, int* status, cudaStre
     L.n = n; L.num_jobs = m; L.status = status;
     for (int q = 0; q < m; ++q) L.max_cols = std::max(L.max_cols, jobs[first + q].N);
     const uint32_t a_bytes = TILE_M * KB * 4, b_bytes = (uint32_t)L.max_cols * KB * 4;
-    const uint32_t stage_bytes = 2 * a_bytes + 2 * b_bytes;
+    uint32_t stage_bytes = 2 * a_bytes + 2 * b_bytes;
     L.stages = (int)std::min<size_t>(8, (220 * 1024 - 1024) / stage_bytes);
+    {   // A through tensor memory when at least four stages of 64 columns fit beside the two accumulators
+      const uint32_t sb = a_bytes + 2 * b_bytes;
+      const int st = (int)std::min<size_t>(std::min<size_t>(8, (220 * 1024 - 1024) / sb), (512 - 2 * L.max_cols) / 64);
+      if (st >= 4 && mix_a_in_tmem()) {
+        L.a_in_tmem = 1;
+        L.stages = st;
+        stage_bytes = sb;
+      }
+    }
     if (L.stages < 2) return fail(EQT_ERR_UNSUPPORTED, "tile too wide for the shared-memory ring");
     L.tmem_cols = 32;
-    while (L.tmem_cols < 2 * L.max_cols) L.tmem_cols <<= 1;
+    while (L.tmem_cols < 2 * L.max_cols + (L.a_in_tmem ? 64 * L.stages : 0)) L.tmem_cols <<= 1;
     int64_t total = 0;
     for (int q = 0; q < m; ++q) {
       const GemmJob& j = jobs[first + q];
