@@ -1,0 +1,40 @@
+"""RMS normalisation of equivariant features (mirrors ``equitorch/nn/functional/normalization.py:8-160``)."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch import Tensor
+
+from ...structs import IrrepsInfo
+from .activations import irrep_scale_infos
+from .norm import batch_mean_squared_norm, channel_mean_squared_norm
+from .sparse_product import sparse_mul, sparse_vecsca
+
+
+def batch_rms_norm(input: Tensor, running_squared_norm: Tensor, irreps_info: IrrepsInfo, weight: Optional[Tensor] = None,
+                   scaled: bool = True, training: bool = False, momentum: float = 0.1, eps: float = 1e-05) -> Tensor:
+    """``out[n, i, c] = x[n, i, c] * weight[k, c] / sqrt(stat[k, c] + eps)``, ``k = irrep(i)``; ``stat`` is the
+    batch mean of the (scaled) squared norms when training (``running_squared_norm`` is updated in place),
+    else ``running_squared_norm``."""
+    if training:
+        stat = batch_mean_squared_norm(input, irreps_info, scaled)
+        running_squared_norm.data.lerp_(stat.detach().to(running_squared_norm.dtype), momentum)
+    else:
+        stat = running_squared_norm
+    scale = torch.rsqrt(stat + eps)
+    if weight is not None:
+        scale = weight * scale
+    fwd, bwd1, bwd2 = irrep_scale_infos(irreps_info)
+    return sparse_mul(input, scale.to(input.dtype), fwd, bwd1, bwd2)
+
+
+def layer_rms_norm(input_tensor: Tensor, irreps_info: IrrepsInfo, weight: Optional[Tensor] = None, scaled: bool = True,
+                   eps: float = 1e-05) -> Tensor:
+    """``out[n, i, c] = x[n, i, c] * weight[k, c] / sqrt(mean_c |x[n, irrep k]|^2 (/ dim_k) + eps)``."""
+    rsigma = torch.rsqrt(channel_mean_squared_norm(input_tensor, irreps_info, scaled) + eps)      # (N, K)
+    fwd, bwd1, bwd2 = irrep_scale_infos(irreps_info)
+    out = sparse_vecsca(input_tensor, rsigma, fwd, bwd1, bwd2)
+    if weight is not None:
+        out = sparse_mul(out, weight.to(out.dtype), fwd, bwd1, bwd2)
+    return out
