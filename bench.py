@@ -176,18 +176,66 @@ def run_reference(args):
 
 
 # ----------------------------------------------------------------------------------------------
+def run_epilogue(args):
+    """Side measurement (one GPU): the layers that follow the tensor product in a message-passing block -
+    Gate -> BatchRMSNorm -> LayerRMSNorm, forward + backward - on the node features of cfg5."""
+    from equitorch_b200 import nn as enn
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    nodes, k = 100_000, L_MAX + 1
+    gen = torch.Generator().manual_seed(3)
+    x = torch.randn(nodes, DIM, CHANNELS, generator=gen).to(dev).requires_grad_(True)
+    gates = torch.randn(nodes, k, CHANNELS, generator=gen).to(dev).requires_grad_(True)
+    cot = torch.randn(nodes, DIM, CHANNELS, generator=gen).to(dev)
+    gate = enn.Gate(IRREPS, activation=torch.nn.Sigmoid()).to(dev)
+    bn = enn.BatchRMSNorm(IRREPS, CHANNELS).to(dev).train()
+    ln = enn.LayerRMSNorm(IRREPS, CHANNELS).to(dev)
+    params = [x, gates, bn.weight, ln.weight]
+
+    def step():
+        out = ln(bn(gate(x, gates)))
+        return torch.autograd.grad(out, params, cot)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize(dev)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        step()
+    t1.record()
+    torch.cuda.synchronize(dev)
+    ms = t0.elapsed_time(t1) / max(1, args.steps)
+    feat = nodes * DIM * CHANNELS * 4
+    # minimal traffic: each of the three layers reads its input and writes its output forward, and reads input +
+    # output gradient and writes the input gradient backward (statistics and gates are 4/16 of a feature tensor)
+    algorithmic = 3 * (2 + 3) * feat + 4 * nodes * k * CHANNELS * 4
+    pk = peaks()
+    print(json.dumps({
+        "metric": "nodes/s, Gate -> BatchRMSNorm -> LayerRMSNorm fwd+bwd (lmax=3, C=64)", "value": nodes / (ms * 1e-3),
+        "unit": "nodes/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "epilogue: 100k nodes x 16 components x 64 channels", "l2": "working set >> 126 MB L2"},
+        "roofline": {"bound": "hbm", "achieved": round(algorithmic / (ms * 1e-3) / 1e9, 1), "peak": pk["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(algorithmic / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4),
+                     "peak_source": pk["source"], "algorithmic_bytes_per_step": algorithmic, "traffic": None},
+    }))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="cfg5", choices=["cfg5", "cfg2", "cfg5q"])
+    ap.add_argument("--workload", default="cfg5", choices=["cfg5", "cfg2", "cfg5q", "epilogue"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time the eager step only (no CUDA-graph replay)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.workload == "epilogue":
+        return run_epilogue(args)
 
     import torch.distributed as dist
     from equitorch_b200 import _lib, _profile
