@@ -78,6 +78,10 @@ SIGNATURES = {
     "eqt_wgrad_tc_static_capacity": (C.c_int64, []),
     "eqt_pack_weights": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_int32,
                                    C.c_void_p, C.c_void_p, C.c_void_p]),
+    "eqt_irrep_scale": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,
+                                  C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
+    "eqt_irrep_dot": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,
+                                C.c_int32, C.c_int32, C.c_void_p]),
     "eqt_last_error": (C.c_char_p, []),
     "eqt_version": (C.c_int, []),
     "eqt_launch_count": (C.c_int64, []),

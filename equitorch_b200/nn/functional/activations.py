@@ -3,17 +3,18 @@ from __future__ import annotations
 
 from torch import Tensor
 
-from ...structs import IrrepsInfo, SparseProductInfo
-from .sparse_product import sparse_mul
-
-
-def irrep_scale_infos(irreps_info: IrrepsInfo):
-    """Tables of ``out[.., i, c] = x[.., i, c] * s[.., irrep(i), c]`` and of its two gradients."""
-    return (SparseProductInfo(index2=irreps_info.irrep_index), SparseProductInfo(index1=irreps_info.irrep_index),
-            SparseProductInfo(seg_out=irreps_info.irrep_seg))
+from ...ops.irrep_ops import PER_SAMPLE_CHANNEL, SHARED
+from ...structs import IrrepsInfo
+from ._irrep import irrep_scale
 
 
 def gating(input: Tensor, gates: Tensor, irreps_info: IrrepsInfo) -> Tensor:
-    """``out[n, i, c] = input[n, i, c] * gates[(n,) irrep(i), c]``; one fused pass forward, one per gradient."""
-    fwd, bwd1, bwd2 = irrep_scale_infos(irreps_info)
-    return sparse_mul(input, gates, fwd, bwd1, bwd2)
+    """``out[n, i, c] = input[n, i, c] * gates[(n,) irrep(i), c]``; ``gates`` is (N, num_irreps, C) or, shared
+    by the batch, (num_irreps, C).  One streaming pass forward, one per gradient."""
+    lead = input.shape[:-2]
+    x = input.reshape(-1, *input.shape[-2:])
+    if gates.ndim == 2:
+        out = irrep_scale(x, gates, irreps_info, SHARED)
+    else:
+        out = irrep_scale(x, gates.reshape(-1, *gates.shape[-2:]), irreps_info, PER_SAMPLE_CHANNEL)
+    return out.reshape(*lead, *out.shape[-2:])

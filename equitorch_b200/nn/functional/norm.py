@@ -1,8 +1,7 @@
 """Per-irrep norms (mirrors ``equitorch/nn/functional/norm.py:14-276``).
 
-The reduction over the components of an irrep is the segmented form of the sparse ``mul`` kernel
-(``x * x`` summed over ``irrep_seg``): one pass over the features, no ``x**2`` intermediate.  Its adjoint
-is the indexed form of the same kernel, which the autograd rule of ``sparse_mul`` supplies.
+The reduction over the components of an irrep is one streaming pass (``irrep_dot`` of the features with
+themselves, no ``x**2`` intermediate); its adjoint is ``irrep_scale``.
 """
 from __future__ import annotations
 
@@ -10,25 +9,14 @@ import torch
 from torch import Tensor
 from torch.autograd import Function
 
-from ...structs import IrrepsInfo, SparseProductInfo
-from .sparse_product import sparse_mul
-
-
-def _reduce_infos(irreps_info: IrrepsInfo):
-    return (SparseProductInfo(seg_out=irreps_info.irrep_seg), SparseProductInfo(index2=irreps_info.irrep_index),
-            SparseProductInfo(index1=irreps_info.irrep_index))
-
-
-def _as3d(x: Tensor):
-    """(..., D, C) -> (N, D, C) and the leading shape."""
-    return x.reshape(-1, x.shape[-2], x.shape[-1]), x.shape[:-2]
+from ...structs import IrrepsInfo
+from ._irrep import irrep_dot
 
 
 def _sum_squares(x: Tensor, irreps_info: IrrepsInfo) -> Tensor:
-    x3, lead = _as3d(x)
-    fwd, bwd1, bwd2 = _reduce_infos(irreps_info)
-    out = sparse_mul(x3, x3, fwd, bwd1, bwd2)
-    return out.reshape(*lead, out.shape[-2], out.shape[-1])
+    x3 = x.reshape(-1, x.shape[-2], x.shape[-1])
+    out = irrep_dot(x3, x3, irreps_info)
+    return out.reshape(*x.shape[:-2], out.shape[-2], out.shape[-1])
 
 
 def squared_norm(input_tensor: Tensor, irreps_info: IrrepsInfo, scaled: bool = True) -> Tensor:
@@ -65,13 +53,5 @@ def channel_mean_squared_norm(input_tensor: Tensor, irreps_info: IrrepsInfo, sca
 
 
 def batch_mean_squared_norm(input_tensor: Tensor, irreps_info: IrrepsInfo, scaled: bool = True) -> Tensor:
-    """Mean over the batch of the squared norms: (N, D, C) -> (num_irreps, C).
-
-    The batch sum is taken inside the kernel (``out_accumulated``), so the (N, num_irreps, C) intermediate
-    is never written.
-    """
-    if input_tensor.ndim != 3:
-        return squared_norm(input_tensor, irreps_info, scaled).mean(dim=0)
-    fwd, bwd1, bwd2 = _reduce_infos(irreps_info)
-    out = sparse_mul(input_tensor, input_tensor, fwd, bwd1, bwd2, True) / input_tensor.shape[0]
-    return out * irreps_info.rdims.unsqueeze(-1) if scaled else out
+    """Mean over the batch of the squared norms: (N, D, C) -> (num_irreps, C)."""
+    return squared_norm(input_tensor, irreps_info, scaled).mean(dim=0)

@@ -6,10 +6,10 @@ from typing import Optional
 import torch
 from torch import Tensor
 
+from ...ops.irrep_ops import PER_SAMPLE, SHARED
 from ...structs import IrrepsInfo
-from .activations import irrep_scale_infos
+from ._irrep import irrep_scale
 from .norm import batch_mean_squared_norm, channel_mean_squared_norm
-from .sparse_product import sparse_mul, sparse_vecsca
 
 
 def batch_rms_norm(input: Tensor, running_squared_norm: Tensor, irreps_info: IrrepsInfo, weight: Optional[Tensor] = None,
@@ -25,16 +25,14 @@ def batch_rms_norm(input: Tensor, running_squared_norm: Tensor, irreps_info: Irr
     scale = torch.rsqrt(stat + eps)
     if weight is not None:
         scale = weight * scale
-    fwd, bwd1, bwd2 = irrep_scale_infos(irreps_info)
-    return sparse_mul(input, scale.to(input.dtype), fwd, bwd1, bwd2)
+    return irrep_scale(input, scale.to(input.dtype), irreps_info, SHARED)
 
 
 def layer_rms_norm(input_tensor: Tensor, irreps_info: IrrepsInfo, weight: Optional[Tensor] = None, scaled: bool = True,
                    eps: float = 1e-05) -> Tensor:
     """``out[n, i, c] = x[n, i, c] * weight[k, c] / sqrt(mean_c |x[n, irrep k]|^2 (/ dim_k) + eps)``."""
     rsigma = torch.rsqrt(channel_mean_squared_norm(input_tensor, irreps_info, scaled) + eps)      # (N, K)
-    fwd, bwd1, bwd2 = irrep_scale_infos(irreps_info)
-    out = sparse_vecsca(input_tensor, rsigma, fwd, bwd1, bwd2)
+    out = irrep_scale(input_tensor, rsigma, irreps_info, PER_SAMPLE)
     if weight is not None:
-        out = sparse_mul(out, weight.to(out.dtype), fwd, bwd1, bwd2)
+        out = irrep_scale(out, weight.to(out.dtype), irreps_info, SHARED)
     return out

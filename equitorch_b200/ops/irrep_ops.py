@@ -1,0 +1,53 @@
+"""Per-irrep streaming operators (operator layer over ``eqt_irrep_scale`` / ``eqt_irrep_dot``)."""
+from __future__ import annotations
+
+import torch
+from torch import Tensor
+
+from .. import _lib
+
+#: layout of the scale operand of :func:`irrep_scale`
+PER_SAMPLE_CHANNEL, SHARED, PER_SAMPLE = 0, 1, 2
+
+
+def _check(x: Tensor) -> None:
+    if x.ndim != 3:
+        raise ValueError(f"features must be (N, components, channels), got {tuple(x.shape)}")
+    if x.dtype not in (torch.float32, torch.float64):
+        raise TypeError(f"float32 or float64 features expected, got {x.dtype}")
+
+
+def irrep_scale(x: Tensor, s: Tensor, irrep_index: Tensor, mode: int) -> Tensor:
+    """``out[n, i, c] = x[n, i, c] * s(n, irrep_index[i], c)`` with ``s`` of shape (N, K, C) (mode 0), (K, C)
+    (mode 1) or (N, K) (mode 2)."""
+    _check(x)
+    dev = _lib.require_cuda(x, s, irrep_index)
+    x, s = x.contiguous(), s.to(x.dtype).contiguous()
+    n, d, c = x.shape
+    k = s.shape[-2] if mode != PER_SAMPLE else s.shape[-1]
+    want = {PER_SAMPLE_CHANNEL: (n, k, c), SHARED: (k, c), PER_SAMPLE: (n, k)}[mode]
+    if tuple(s.shape) != want:
+        raise ValueError(f"scale operand of mode {mode} must be {want}, got {tuple(s.shape)}")
+    out = torch.empty_like(x)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().eqt_irrep_scale(x.data_ptr(), s.data_ptr(), out.data_ptr(), irrep_index.data_ptr(), n, d, k, c,
+                                              mode, _lib.DTYPE_CODE[x.dtype], _lib.stream_ptr(dev)), "eqt_irrep_scale")
+    return out
+
+
+def irrep_dot(a: Tensor, b: Tensor, irrep_seg: Tensor) -> Tensor:
+    """``out[n, k, c] = sum_{i in irrep k} a[n, i, c] * b[n, i, c]`` -> (N, num_irreps, C)."""
+    _check(a)
+    dev = _lib.require_cuda(a, b, irrep_seg)
+    if a.shape != b.shape or a.dtype != b.dtype:
+        raise ValueError("operands of irrep_dot must have the same shape and dtype")
+    same = a is b
+    a = a.contiguous()
+    b = a if same else b.contiguous()
+    n, d, c = a.shape
+    k = irrep_seg.numel() - 1
+    out = torch.empty(n, k, c, dtype=a.dtype, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().eqt_irrep_dot(a.data_ptr(), b.data_ptr(), out.data_ptr(), irrep_seg.data_ptr(), n, d, k, c,
+                                            _lib.DTYPE_CODE[a.dtype], _lib.stream_ptr(dev)), "eqt_irrep_dot")
+    return out

@@ -270,6 +270,24 @@ int eqt_version(void);
 /* Kernel launches issued by this library in the calling process since load (for benchmarks). */
 int64_t eqt_launch_count(void);
 
+/*
+ * Per-irrep streaming kernels behind Gate, the norms and the RMS normalisations (float32 / float64).
+ *   eqt_irrep_scale: out[n, i, c] = x[n, i, c] * s(n, irrep_index[i], c); s_mode 0: s is (n, k, c), 1: s is (k, c)
+ *                    shared by all samples, 2: s is (n, k), one scalar per sample and irrep.
+ *                    replaces: gating, equitorch/nn/functional/activations.py:31-36, and the scaling steps of
+ *                    batch_rms_norm / layer_rms_norm, equitorch/nn/functional/normalization.py:58-63,147-156
+ *                    (sparse_mul / sparse_vecsca with index2 = irrep_index).
+ *   eqt_irrep_dot:   out[n, kk, c] = sum_{i in [irrep_seg[kk], irrep_seg[kk+1])} a[n, i, c] * b[n, i, c]; a == b
+ *                    gives the squared norms.  replaces: segment(input.pow(2), irrep_seg),
+ *                    equitorch/nn/functional/norm.py:26,75,143,206, and the gate-gradient reduction
+ *                    (sparse_mul with seg_out = irrep_seg).
+ * x / a / b are (n, d, c) contiguous, d <= 1024 components in k irreps.
+ */
+int eqt_irrep_scale(const void* x, const void* s, void* out, const int64_t* irrep_index, int64_t n, int32_t d,
+                    int32_t k, int32_t c, int32_t s_mode, int32_t dtype, void* stream);
+int eqt_irrep_dot(const void* a, const void* b, void* out, const int64_t* irrep_seg, int64_t n, int32_t d,
+                  int32_t k, int32_t c, int32_t dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
