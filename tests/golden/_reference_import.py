@@ -20,7 +20,9 @@ import types
 
 import torch
 
-REFERENCE_ROOT = os.environ.get("EQUITORCH_REFERENCE_ROOT", "/root/reference")
+# the checkout is looked for beside this repository unless EQUITORCH_REFERENCE_ROOT says otherwise
+_REPO = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+REFERENCE_ROOT = os.environ.get("EQUITORCH_REFERENCE_ROOT", os.path.join(os.path.dirname(_REPO), "reference"))
 
 
 def _segment(src: torch.Tensor, ptr: torch.Tensor, reduce: str = "sum") -> torch.Tensor:
