@@ -1,7 +1,8 @@
 """Benchmark of the hot path: edges/s of the Clebsch-Gordan tensor-product layer, forward + backward
 (l_max = 3, 64 channels, full 64 -> 64 channel mixing per path), on N GPUs of one box.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg5|cfg2] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg5|cfg5q|cfg2|epilogue] [--impl ours|reference]
+                    [--no-graph] [--no-cpu-baseline]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
 One step = one pass of the layer over one synthetic graph: spherical harmonics of the edge vectors,
@@ -16,6 +17,12 @@ Workloads (seeded synthetic data, shapes of the benchmark configurations):
   cfg5q a quarter-size cfg5 (25k nodes, ~500k edges) for profiler captures.
   cfg2  200k edges with uniformly random sources over 10k nodes (single GPU).  Its node table fits in
         L2, so L2 is flushed between steps and every step is timed on its own.
+  epilogue  side measurement, one GPU: Gate -> BatchRMSNorm -> LayerRMSNorm forward + backward on 100k x 16 x 64
+        node features (its own JSON line; not the metric of the benchmark).
+
+The timed region runs twice: eagerly with CUDA events around every kernel (the per-kernel table and
+``eager_ms_per_step``) and as replays of a CUDA graph of the same step (``value`` / ``ms_per_step``; at small
+per-GPU sizes the eager step is bound by the Python launch overhead, ``host_enqueue_ms_per_step``).
 
 Rank 0 prints ONE JSON line.  ``value`` is device-timed with inputs resident in HBM; ``e2e`` moves the
 step's inputs from pinned host memory and the result back inside the timed region; ``roofline``

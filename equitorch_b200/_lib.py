@@ -82,6 +82,11 @@ SIGNATURES = {
                                   C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "eqt_irrep_dot": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,
                                 C.c_int32, C.c_int32, C.c_void_p]),
+    "eqt_layer_rms_num_partials": (C.c_int, [C.c_int64]),
+    "eqt_layer_rms_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32,
+                                        C.c_int32, C.c_int32, C.c_int32, C.c_double, C.c_int32, C.c_void_p]),
+    "eqt_layer_rms_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                         C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "eqt_last_error": (C.c_char_p, []),
     "eqt_version": (C.c_int, []),
     "eqt_launch_count": (C.c_int64, []),

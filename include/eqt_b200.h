@@ -288,6 +288,25 @@ int eqt_irrep_scale(const void* x, const void* s, void* out, const int64_t* irre
 int eqt_irrep_dot(const void* a, const void* b, void* out, const int64_t* irrep_seg, int64_t n, int32_t d,
                   int32_t k, int32_t c, int32_t dtype, void* stream);
 
+/*
+ * Fused LayerRMSNorm (float32 / float64): per sample n and irrep k
+ *   rsigma[n, k] = (mean_c sum_{i in k} x[n, i, c]^2 (/ dim_k if scaled) + eps)^-1/2
+ *   out[n, i, c] = x[n, i, c] * rsigma[n, k(i)] * weight[k(i), c]            (weight may be NULL)
+ * in one pass (one warp per sample), and its backward: grad_x, plus per-warp partial sums of grad_weight,
+ * grad_weight_partial (eqt_layer_rms_num_partials(n), k, c), which the caller sums over the first dimension
+ * (NULL = not wanted).  Needs k <= 16, C / 4 (float32) or C / 2 (float64) dividing 32, 16-byte aligned tensors;
+ * EQT_ERR_UNSUPPORTED otherwise.
+ * replaces: layer_rms_norm, equitorch/nn/functional/normalization.py:112-160 (channel_mean_squared_norm,
+ * sparse_vecsca, sparse_mul and their backward passes).
+ */
+int eqt_layer_rms_num_partials(int64_t n);
+int eqt_layer_rms_forward(const void* x, const void* weight, void* out, void* rsigma, const int64_t* irrep_seg,
+                          int64_t n, int32_t d, int32_t k, int32_t c, int32_t scaled, double eps, int32_t dtype,
+                          void* stream);
+int eqt_layer_rms_backward(const void* x, const void* grad_out, const void* weight, const void* rsigma, void* grad_x,
+                           void* grad_weight_partial, const int64_t* irrep_seg, int64_t n, int32_t d, int32_t k,
+                           int32_t c, int32_t scaled, int32_t dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

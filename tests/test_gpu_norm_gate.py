@@ -94,3 +94,14 @@ def test_layer_sizes_against_oracle():
     for a, b in zip(got, [ref, *gref]):
         err = float((a.detach().double().cpu() - b.detach()).abs().max() / b.detach().abs().max())
         assert err < 1e-5
+
+
+@pytest.mark.parametrize("key", sorted(k for k in GOLD["cases"] if "/layer_rms" in k))
+def test_layer_rms_unfused_composition(key, monkeypatch):
+    """The composition of per-irrep operators (used for higher-order derivatives) gives the same result."""
+    from equitorch_b200.nn.functional import normalization
+    monkeypatch.setattr(normalization, "FUSED_LAYER_RMS", False)
+    case = {k: (v.to(DEV) if torch.is_tensor(v) else v) for k, v in GOLD["cases"][key].items()}
+    out, grads, _ = run_case(key, case, _impl(key.split("/")[0], torch.float64))
+    assert float((out.detach() - case["out"]).abs().max()) <= 1e-11
+    assert float((grads[0] - case["gx"]).abs().max()) <= 1e-11 * max(1.0, float(case["gx"].abs().max()))
