@@ -29,7 +29,6 @@ def _impl(name, dtype):
         torch.set_default_dtype(prev)
 
     def gate(x, g, dims, activation, irrep_wise=True):
-        act = None if activation is None else types.SimpleNamespace(__call__=activation)
         mod = enn.Gate(ir, activation=activation, irrep_wise=irrep_wise).to(DEV)
         mod.irreps_info = info
         return mod(x, g)
