@@ -281,8 +281,8 @@ def main():
     sh = enn.SphericalHarmonics(L_MAX)
     x_dev = x_host.to(dev).requires_grad_(True)
     vec_dev = vec_host.to(dev).requires_grad_(True)
-    loss_host = torch.empty(1, dtype=torch.float32).pin_memory()
-    gw_host = torch.empty(PATHS, CHANNELS, CHANNELS).pin_memory()
+    loss_host = torch.empty(2, dtype=torch.float32).pin_memory()             # two slots: results are read one step late
+    gw_host = torch.empty(2, PATHS, CHANNELS, CHANNELS).pin_memory()
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev) if args.workload == "cfg2" else None
 
     def step(x, vec):
@@ -389,22 +389,36 @@ def main():
             bufs[slot][1].copy_(vec_host, non_blocking=True)
             ready[slot].record(copy_stream)
 
+    read_back = [torch.cuda.Event() for _ in range(2)]
+    results = []
+
+    def e2e_steps(count):
+        enqueue_inputs(0)
+        for i in range(count):
+            if i + 1 < count:
+                enqueue_inputs(i + 1)
+            main_stream.wait_event(ready[i % 2])
+            if graphed is not None:
+                out, gx, gv, gw = graphed[i % 2].replay()
+            else:
+                out, gx, gv, gw = step(*bufs[i % 2])
+            consumed[i % 2].record(main_stream)
+            # the step's result (loss = <out, cotangent>, weight gradient) goes to the host every step; the host
+            # reads it while the next step is already running, so the device never waits for Python
+            loss_host[i % 2: i % 2 + 1].copy_(torch.dot(out.reshape(-1), cot.reshape(-1)).reshape(1), non_blocking=True)
+            gw_host[i % 2].copy_(gw, non_blocking=True)
+            read_back[i % 2].record(main_stream)
+            if i > 0:
+                read_back[(i - 1) % 2].synchronize()
+                results.append(float(loss_host[(i - 1) % 2]))
+        read_back[(count - 1) % 2].synchronize()
+        results.append(float(loss_host[(count - 1) % 2]))
+
+    e2e_steps(2)                      # untimed: first use of the copy stream, the reduction and the host buffers
     barrier()
     e0_, e1_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0_.record()
-    enqueue_inputs(0)
-    for i in range(args.steps):
-        if i + 1 < args.steps:
-            enqueue_inputs(i + 1)
-        main_stream.wait_event(ready[i % 2])
-        if graphed is not None:
-            out, gx, gv, gw = graphed[i % 2].replay()
-        else:
-            out, gx, gv, gw = step(*bufs[i % 2])
-        consumed[i % 2].record(main_stream)
-        loss_host.copy_((out * cot).sum().reshape(1), non_blocking=True)
-        gw_host.copy_(gw, non_blocking=True)
-        main_stream.synchronize()
+    e2e_steps(args.steps)
     e1_.record()
     barrier()
     e2e_ms = e0_.elapsed_time(e1_)
@@ -471,7 +485,7 @@ def main():
         "e2e": {"value": e2e_value, "unit": "edges/s", "ms_per_step": e2e_ms / steps,
                 "h2d_bytes_per_step": int(x_host.numel() * 4 + vec_host.numel() * 4) * world if world == 1
                 else int(x_all.numel() * 4 + graph.edge_vec.numel() * 4),
-                "d2h_bytes_per_step": int(4 + gw_host.numel() * 4) * world},
+                "d2h_bytes_per_step": int(4 + gw_host[0].numel() * 4) * world},
         "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "kernels": table,
         "host_enqueue_ms_per_step": (round(host_enqueue_ms / steps, 3) if host_enqueue_ms is not None else None),
         "cuda_graph": graphed is not None, "cuda_graph_error": graph_error,
