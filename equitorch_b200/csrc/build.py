@@ -40,7 +40,8 @@ def sources():
 
 
 def _stale() -> bool:
-    if not os.path.exists(LIB_PATH) or not os.path.exists(os.path.join(HERE, "generated", "tp_specs.inc")):
+    if not os.path.exists(LIB_PATH) or not os.path.exists(os.path.join(HERE, "generated", "tp_specs.inc")) \
+            or not os.path.exists(os.path.join(HERE, "generated", "sh_specs.inc")):
         return True
     built = os.path.getmtime(LIB_PATH)
     deps = sources() + glob.glob(os.path.join(HERE, "*.cuh")) + glob.glob(os.path.join(HERE, "*.inc")) + glob.glob(os.path.join(HERE, "*.py")) \
@@ -52,8 +53,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
     """Build if sources are newer than the library; returns the library path."""
     if not force and not _stale():
         return LIB_PATH
+    from .gen_sh_specs import generate as generate_sh
     from .gen_tp_specs import generate
     generate()
+    generate_sh()
     os.makedirs(LIB_DIR, exist_ok=True)
     obj_dir = os.path.join(LIB_DIR, "obj")
     os.makedirs(obj_dir, exist_ok=True)

@@ -7,6 +7,8 @@
 namespace eqt {
 namespace {
 
+#include "generated/sh_specs.inc"
+
 struct ShTab {
   const int32_t* ptr;
   const int32_t* m_out;
@@ -115,6 +117,101 @@ __global__ void sh_backward_kernel(const T* __restrict__ xyz, const T* __restric
   }
 }
 
+template <typename Kern>
+int configure_smem(Kern kern, size_t bytes) {
+  if (bytes > 48 * 1024) {
+    if (bytes > 227 * 1024) return fail(EQT_ERR_UNSUPPORTED, "l_max needs %zu bytes of shared memory", bytes);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) return fail(EQT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  }
+  return EQT_OK;
+}
+
+// Small l_max: the recurrence as straight-line code on registers (generated/sh_specs.inc).  The forward kernel
+// still goes through a shared-memory transpose so that a block writes its slab of the output contiguously.
+template <typename T, int LMAX>
+__global__ void __launch_bounds__(256) sh_forward_unrolled_kernel(const T* __restrict__ xyz, T* __restrict__ out, int64_t n,
+                                                                  int normalize, typename Acc<T>::type out_scale) {
+  using A = typename Acc<T>::type;
+  using U = ShUnrolled<A, LMAX>;
+  constexpr int K = U::K;
+  extern __shared__ unsigned char smem_raw[];
+  A* col = reinterpret_cast<A*>(smem_raw);
+  const int B = blockDim.x, tid = threadIdx.x;
+  for (int64_t base = (int64_t)blockIdx.x * B; base < n; base += (int64_t)gridDim.x * B) {
+    const int64_t pt = base + tid;
+    if (pt < n) {
+      A r[3] = {ld(xyz + pt * 3), ld(xyz + pt * 3 + 1), ld(xyz + pt * 3 + 2)};
+      if (normalize) {
+        const A inv = A(1) / max(sqrt(r[0] * r[0] + r[1] * r[1] + r[2] * r[2]), A(1e-12));
+        r[0] *= inv; r[1] *= inv; r[2] *= inv;
+      }
+      A y[K];
+      U::forward(r, y);
+#pragma unroll
+      for (int k = 0; k < K; ++k) col[k * B + tid] = y[k] * out_scale;
+    }
+    __syncthreads();
+    const int64_t rows = min((int64_t)B, n - base);
+    for (int64_t q = tid; q < rows * K; q += B) {
+      const int th = q / K, comp = q % K;
+      st(out + base * K + q, col[comp * B + th]);
+    }
+    __syncthreads();
+  }
+}
+
+template <typename T, int LMAX>
+__global__ void __launch_bounds__(256) sh_backward_unrolled_kernel(const T* __restrict__ xyz, const T* __restrict__ gout,
+                                                                   T* __restrict__ gxyz, int64_t n, int normalize,
+                                                                   typename Acc<T>::type out_scale) {
+  using A = typename Acc<T>::type;
+  using U = ShUnrolled<A, LMAX>;
+  constexpr int K = U::K;
+  for (int64_t pt = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; pt < n; pt += (int64_t)gridDim.x * blockDim.x) {
+    A u[3] = {ld(xyz + pt * 3), ld(xyz + pt * 3 + 1), ld(xyz + pt * 3 + 2)};
+    A r[3] = {u[0], u[1], u[2]};
+    A norm = A(1);
+    if (normalize) {
+      norm = max(sqrt(u[0] * u[0] + u[1] * u[1] + u[2] * u[2]), A(1e-12));
+      r[0] /= norm; r[1] /= norm; r[2] /= norm;
+    }
+    A go[K], g[3];
+#pragma unroll
+    for (int k = 0; k < K; ++k) go[k] = ld(gout + pt * K + k);
+    U::backward(r, go, g);
+    g[0] *= out_scale; g[1] *= out_scale; g[2] *= out_scale;
+    if (normalize) {
+      // v = u / max(|u|, eps):  dv = (I - v v^T) / |u| above eps, I / eps below
+      const A un = sqrt(u[0] * u[0] + u[1] * u[1] + u[2] * u[2]);
+      if (un > A(1e-12)) {
+        const A dot = g[0] * r[0] + g[1] * r[1] + g[2] * r[2];
+        g[0] = (g[0] - r[0] * dot) / norm; g[1] = (g[1] - r[1] * dot) / norm; g[2] = (g[2] - r[2] * dot) / norm;
+      } else {
+        g[0] /= norm; g[1] /= norm; g[2] /= norm;
+      }
+    }
+    st(gxyz + pt * 3, g[0]); st(gxyz + pt * 3 + 1, g[1]); st(gxyz + pt * 3 + 2, g[2]);
+  }
+}
+
+template <typename T, int LMAX>
+int sh_launch_unrolled(bool backward, const void* xyz, const void* gout, void* out, int64_t n, int normalize, double out_scale,
+                       cudaStream_t s) {
+  using A = typename Acc<T>::type;
+  constexpr int K = (LMAX + 1) * (LMAX + 1);
+  const unsigned grid = flat_grid(n, 256, 148 * 8);
+  if (backward) {
+    sh_backward_unrolled_kernel<T, LMAX><<<grid, 256, 0, s>>>(static_cast<const T*>(xyz), static_cast<const T*>(gout),
+                                                              static_cast<T*>(out), n, normalize, (A)out_scale);
+    return check_launch("sh_backward_unrolled_kernel");
+  }
+  if (int rc = configure_smem(sh_forward_unrolled_kernel<T, LMAX>, sizeof(A) * K * 256)) return rc;
+  sh_forward_unrolled_kernel<T, LMAX><<<grid, 256, sizeof(A) * K * 256, s>>>(static_cast<const T*>(xyz), static_cast<T*>(out), n,
+                                                                             normalize, (A)out_scale);
+  return check_launch("sh_forward_unrolled_kernel");
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) segment_sum_kernel(const T* __restrict__ in, const int64_t* __restrict__ ptr,
                                                           const int64_t* __restrict__ perm, T* __restrict__ out,
@@ -150,21 +247,18 @@ int check_table(const eqt_sh_table* t) {
   return EQT_OK;
 }
 
-template <typename Kern>
-int configure_smem(Kern kern, size_t bytes) {
-  if (bytes > 48 * 1024) {
-    if (bytes > 227 * 1024) return fail(EQT_ERR_UNSUPPORTED, "l_max needs %zu bytes of shared memory", bytes);
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-    if (e != cudaSuccess) return fail(EQT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-  }
-  return EQT_OK;
-}
-
 template <typename T>
 int sh_launch(bool backward, const void* xyz, const void* gout, void* out, int64_t n, const eqt_sh_table* t,
               int normalize, double out_scale, cudaStream_t s) {
   using A = typename Acc<T>::type;
   if (n == 0) return EQT_OK;
+  switch (t->l_max) {   // straight-line kernels for the degrees generated at build time
+    case 1: return sh_launch_unrolled<T, 1>(backward, xyz, gout, out, n, normalize, out_scale, s);
+    case 2: return sh_launch_unrolled<T, 2>(backward, xyz, gout, out, n, normalize, out_scale, s);
+    case 3: return sh_launch_unrolled<T, 3>(backward, xyz, gout, out, n, normalize, out_scale, s);
+    case 4: return sh_launch_unrolled<T, 4>(backward, xyz, gout, out, n, normalize, out_scale, s);
+    default: break;
+  }
   ShTab tab{t->ptr, t->m_out, t->m_in, t->axis, t->coef, t->l_max};
   const int K = (t->l_max + 1) * (t->l_max + 1), W = 2 * t->l_max + 1;
   const size_t per_thread = sizeof(A) * (backward ? 8 * W : K);
