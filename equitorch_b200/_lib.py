@@ -76,6 +76,7 @@ SIGNATURES = {
     "eqt_wgrad_tc_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32,
                                       C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
     "eqt_wgrad_tc_static_capacity": (C.c_int64, []),
+    "eqt_wgrad_tc_scratch_floats": (C.c_int64, [C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_int32]),
     "eqt_pack_weights": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_int32,
                                    C.c_void_p, C.c_void_p, C.c_void_p]),
     "eqt_irrep_scale": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,

@@ -39,10 +39,14 @@ template <> __device__ __forceinline__ void st<__nv_bfloat16, float>(__nv_bfloat
 
 __host__ __device__ inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
-// Grid size for a flat 1-D launch: enough blocks for `work` items, capped so that one wave of a
-// grid-stride loop fills the 148 SMs a few times over.
-inline unsigned flat_grid(int64_t work, int threads, int max_blocks = 148 * 32) {
+// Number of SMs of the current device (queried once per device ordinal).
+int sm_count();
+
+// Grid size for a flat 1-D launch: enough blocks for `work` items, capped at `blocks_per_sm` blocks per
+// SM of the current device so that one wave of a grid-stride loop fills the GPU a few times over.
+inline unsigned flat_grid(int64_t work, int threads, int blocks_per_sm = 32) {
   int64_t b = ceil_div(work, threads);
+  const int64_t max_blocks = (int64_t)sm_count() * blocks_per_sm;
   if (b < 1) b = 1;
   if (b > max_blocks) b = max_blocks;
   return static_cast<unsigned>(b);

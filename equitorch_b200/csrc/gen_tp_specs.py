@@ -8,7 +8,7 @@ role (see ``OuterPlan``).  Only the *index structure* is baked in; the CG values
 run-time data (``scale``), so path / channel normalisation do not need their own code.
 
 A structure is identified by ``structure_key`` (a hash of T, R, D_feat, D_y and the three
-index columns); ``equitorch_b200.fused`` computes the same key from a layer's tables and
+index columns); ``equitorch_b200.ops.fused_tp_op.TpTable`` computes the same key from a layer's tables and
 falls back to the table-driven kernels when the key is not in the registry.
 
     python -m equitorch_b200.csrc.gen_tp_specs        # rewrites generated/tp_specs.inc

@@ -21,20 +21,23 @@ template <> struct Vec<float, 4> { using type = float4; };
 template <> struct Vec<double, 2> { using type = double2; };
 template <> struct Vec<float, 1> { using type = float; };
 template <> struct Vec<double, 1> { using type = double; };
+template <> struct Vec<__nv_bfloat16, 8> { using type = uint4; };
+template <> struct Vec<__nv_bfloat16, 1> { using type = __nv_bfloat16; };
 
+// V storage elements of type T <-> V values of the arithmetic type (float for bfloat16 storage)
 template <typename T, int V>
-__device__ __forceinline__ void load(const T* p, T (&v)[V]) {
+__device__ __forceinline__ void load(const T* p, typename Acc<T>::type (&v)[V]) {
   const typename Vec<T, V>::type t = __ldg(reinterpret_cast<const typename Vec<T, V>::type*>(p));
   const T* q = reinterpret_cast<const T*>(&t);
 #pragma unroll
-  for (int i = 0; i < V; ++i) v[i] = q[i];
+  for (int i = 0; i < V; ++i) v[i] = static_cast<typename Acc<T>::type>(q[i]);
 }
 template <typename T, int V>
-__device__ __forceinline__ void store(T* p, const T (&v)[V]) {
+__device__ __forceinline__ void store(T* p, const typename Acc<T>::type (&v)[V]) {
   typename Vec<T, V>::type t;
   T* q = reinterpret_cast<T*>(&t);
 #pragma unroll
-  for (int i = 0; i < V; ++i) q[i] = v[i];
+  for (int i = 0; i < V; ++i) q[i] = static_cast<T>(v[i]);
   *reinterpret_cast<typename Vec<T, V>::type*>(p) = t;
 }
 
@@ -53,10 +56,10 @@ __global__ void __launch_bounds__(256) irrep_scale_kernel(const T* __restrict__ 
     const int rem = (int)(idx - row * per_sample);
     const int i = rem / cv, c0 = (rem - i * cv) * V;
     const int kk = kidx[i];
-    T xv[V], sv[V], ov[V];
+    typename Acc<T>::type xv[V], sv[V], ov[V];
     load<T, V>(x + (row * d + i) * c + c0, xv);
     if (s_mode == 2) {
-      const T t = __ldg(s + row * k + kk);
+      const typename Acc<T>::type t = ld(s + row * k + kk);
 #pragma unroll
       for (int q = 0; q < V; ++q) sv[q] = t;
     } else {
@@ -80,11 +83,12 @@ __global__ void __launch_bounds__(256) irrep_dot_kernel(const T* a, const T* b, 
     const int64_t row = idx / per_sample;
     const int rem = (int)(idx - row * per_sample);
     const int kk = rem / cv, c0 = (rem - kk * cv) * V;
-    T acc[V];
+    using A = typename Acc<T>::type;
+    A acc[V];
 #pragma unroll
-    for (int q = 0; q < V; ++q) acc[q] = T(0);
+    for (int q = 0; q < V; ++q) acc[q] = A(0);
     for (int i = seg[kk]; i < seg[kk + 1]; ++i) {
-      T av[V], bv[V];
+      A av[V], bv[V];
       load<T, V>(a + (row * d + i) * c + c0, av);
       if (a == b) {
 #pragma unroll
@@ -103,14 +107,14 @@ template <typename T, int V>
 int run_scale(const void* x, const void* s, void* out, const int64_t* index, int64_t n, int d, int k, int c, int mode,
               cudaStream_t st) {
   const int64_t work = n * d * (c / V);
-  irrep_scale_kernel<T, V><<<flat_grid(work, 256, 148 * 16), 256, 0, st>>>(static_cast<const T*>(x), static_cast<const T*>(s),
+  irrep_scale_kernel<T, V><<<flat_grid(work, 256, 16), 256, 0, st>>>(static_cast<const T*>(x), static_cast<const T*>(s),
                                                                             static_cast<T*>(out), index, n, d, k, c, mode);
   return check_launch("irrep_scale_kernel");
 }
 template <typename T, int V>
 int run_dot(const void* a, const void* b, void* out, const int64_t* seg, int64_t n, int d, int k, int c, cudaStream_t st) {
   const int64_t work = n * k * (c / V);
-  irrep_dot_kernel<T, V><<<flat_grid(work, 256, 148 * 16), 256, 0, st>>>(static_cast<const T*>(a), static_cast<const T*>(b),
+  irrep_dot_kernel<T, V><<<flat_grid(work, 256, 16), 256, 0, st>>>(static_cast<const T*>(a), static_cast<const T*>(b),
                                                                           static_cast<T*>(out), seg, n, d, k, c);
   return check_launch("irrep_dot_kernel");
 }
@@ -118,7 +122,7 @@ int run_dot(const void* a, const void* b, void* out, const int64_t* seg, int64_t
 int check_sizes(int64_t n, int d, int k, int c, int dtype) {
   if (n < 0 || d <= 0 || k <= 0 || c <= 0) return fail(EQT_ERR_BAD_ARGUMENT, "bad sizes");
   if (d > MAX_COMPONENTS || k > d) return fail(EQT_ERR_UNSUPPORTED, "at most %d components, num_irreps <= components", MAX_COMPONENTS);
-  if (dtype != EQT_F32 && dtype != EQT_F64) return fail(EQT_ERR_UNSUPPORTED, "float32 or float64 only");
+  if (dtype != EQT_F32 && dtype != EQT_F64 && dtype != EQT_BF16) return fail(EQT_ERR_UNSUPPORTED, "float32, float64 or bfloat16 only");
   return EQT_OK;
 }
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -139,6 +143,10 @@ extern "C" int eqt_irrep_scale(const void* x, const void* s, void* out, const in
     if (c % 4 == 0 && vec_ok) return run_scale<float, 4>(x, s, out, irrep_index, n, d, k, c, s_mode, st);
     return run_scale<float, 1>(x, s, out, irrep_index, n, d, k, c, s_mode, st);
   }
+  if (dtype == EQT_BF16) {   // bfloat16 storage, float32 arithmetic
+    if (c % 8 == 0 && vec_ok) return run_scale<__nv_bfloat16, 8>(x, s, out, irrep_index, n, d, k, c, s_mode, st);
+    return run_scale<__nv_bfloat16, 1>(x, s, out, irrep_index, n, d, k, c, s_mode, st);
+  }
   if (c % 2 == 0 && vec_ok) return run_scale<double, 2>(x, s, out, irrep_index, n, d, k, c, s_mode, st);
   return run_scale<double, 1>(x, s, out, irrep_index, n, d, k, c, s_mode, st);
 }
@@ -154,6 +162,10 @@ extern "C" int eqt_irrep_dot(const void* a, const void* b, void* out, const int6
   if (dtype == EQT_F32) {
     if (c % 4 == 0 && vec_ok) return run_dot<float, 4>(a, b, out, irrep_seg, n, d, k, c, st);
     return run_dot<float, 1>(a, b, out, irrep_seg, n, d, k, c, st);
+  }
+  if (dtype == EQT_BF16) {
+    if (c % 8 == 0 && vec_ok) return run_dot<__nv_bfloat16, 8>(a, b, out, irrep_seg, n, d, k, c, st);
+    return run_dot<__nv_bfloat16, 1>(a, b, out, irrep_seg, n, d, k, c, st);
   }
   if (c % 2 == 0 && vec_ok) return run_dot<double, 2>(a, b, out, irrep_seg, n, d, k, c, st);
   return run_dot<double, 1>(a, b, out, irrep_seg, n, d, k, c, st);
@@ -300,7 +312,7 @@ template <> struct LrnVec<double> { static constexpr int V = 2; };
 
 int layer_rms_grid(int64_t n) {
   // eight warps per CTA, a few CTAs per SM; each warp walks samples with stride `warps`
-  return (int)std::max<int64_t>(1, std::min<int64_t>((n + 7) / 8, 148 * 8));
+  return (int)std::max<int64_t>(1, std::min<int64_t>((n + 7) / 8, (int64_t)sm_count() * 8));
 }
 
 bool layer_rms_ok(int d, int k, int c, int v) {

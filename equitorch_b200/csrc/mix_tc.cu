@@ -27,8 +27,6 @@
 // Every wait on an mbarrier is bounded; on expiry the kernel raises the status flag, stops
 // issuing work, frees its TMEM and returns.
 #include <algorithm>
-#include <cstdlib>
-#include <string>
 #include <vector>
 
 #include "tc_common.cuh"
@@ -86,21 +84,10 @@ struct GemmJob {
   int64_t out_node_stride, out_m_stride;   // floats
 };
 
-// EQT_MIX_A=smem keeps the split A operand in shared memory (for comparisons); default: tensor memory
-bool mix_a_in_tmem() {
-  static const bool on = [] {
-    const char* v = std::getenv("EQT_MIX_A");
-    return !(v && std::string(v) == "smem");
-  }();
-  return on;
-}
-
 int launch_jobs(const GemmJob* jobs, int count, int64_t n, int* status, cudaStream_t st) {
-  static bool configured = false;
-  if (!configured) {
+  {   // per device / context, so set on every call (a cheap host-side call)
     cudaError_t e = cudaFuncSetAttribute(mix_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     if (e != cudaSuccess) return fail(EQT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    configured = true;
   }
   for (int first = 0; first < count; first += MAX_JOBS) {
     const int m = std::min(MAX_JOBS, count - first);
@@ -113,15 +100,17 @@ int launch_jobs(const GemmJob* jobs, int count, int64_t n, int* status, cudaStre
     {   // A through tensor memory when at least four stages of 64 columns fit beside the two accumulators
       const uint32_t sb = a_bytes + 2 * b_bytes;
       const int st = (int)std::min<size_t>(std::min<size_t>(8, (220 * 1024 - 1024) / sb), (512 - 2 * L.max_cols) / 64);
-      if (st >= 4 && mix_a_in_tmem()) {
+      if (st >= 4) {
         L.a_in_tmem = 1;
         L.stages = st;
         stage_bytes = sb;
       }
     }
     if (L.stages < 2) return fail(EQT_ERR_UNSUPPORTED, "tile too wide for the shared-memory ring");
+    // the epilogue reads accumulators in groups of 32 columns, so the second one is padded to a multiple of 32
+    const int acc_cols = L.max_cols + (L.max_cols + 31) / 32 * 32;
     L.tmem_cols = 32;
-    while (L.tmem_cols < 2 * L.max_cols + (L.a_in_tmem ? 64 * L.stages : 0)) L.tmem_cols <<= 1;
+    while (L.tmem_cols < std::max(acc_cols, 2 * L.max_cols + (L.a_in_tmem ? 64 * L.stages : 0))) L.tmem_cols <<= 1;
     int64_t total = 0;
     for (int q = 0; q < m; ++q) {
       const GemmJob& j = jobs[first + q];
@@ -217,6 +206,50 @@ extern "C" int eqt_mix_tc_transposed(const float* g, const float* w_big, const f
   return launch_jobs(jobs.data(), (int)jobs.size(), n, status, static_cast<cudaStream_t>(stream));
 }
 
+namespace eqt {
+namespace {
+
+// Launch shape of the weight-gradient GEMM of one block: reduction rows per tile, M tiles, node splits and the
+// floats of scratch the per-CTA partial sums need.  Returns an error code for blocks that do not fit.
+struct WgradShape { int npt, m_tiles, splits, stages, chunk_tiles; size_t stage_bytes; int64_t K, need; };
+int wgrad_shape(const eqt_mix_block& blk, int b, int64_t n, int cin, int cout, WgradShape* w) {
+  if (blk.dim <= 0 || blk.dim > TILE_M || blk.paths <= 0) return fail(EQT_ERR_BAD_ARGUMENT, "bad block %d", b);
+  const int b_boxes = cout / 32;
+  const size_t budget = 220 * 1024 - 1024;
+  w->K = (int64_t)blk.paths * cin;                               // M extent of this GEMM
+  w->m_tiles = (int)ceil_div(w->K, 128);
+  // reduction rows per tile: multiple of 8 and of dim, two stages must fit in shared memory
+  const size_t bytes_per_row = 2 * (size_t)(4 + b_boxes) * 128;
+  const int rows_cap = (int)std::min<size_t>(128, budget / 2 / bytes_per_row);
+  int step = 8;
+  for (int d = blk.dim; d % 2 == 0 && step > 1; d /= 2) step /= 2;   // 8 / gcd(dim, 8)
+  w->npt = (rows_cap / blk.dim) / step * step;
+  if (w->npt <= 0) return fail(EQT_ERR_UNSUPPORTED, "irrep with %d components does not fit a reduction tile", blk.dim);
+  w->stage_bytes = bytes_per_row * (size_t)(w->npt * blk.dim);
+  w->stages = (int)std::min<size_t>(4, budget / w->stage_bytes);
+  w->chunk_tiles = std::max(1, 512 / (w->npt * blk.dim));
+  const int64_t tiles = ceil_div(n, w->npt);
+  w->splits = (int)std::max<int64_t>(1, std::min<int64_t>(tiles, sm_count() / w->m_tiles));
+  w->need = (int64_t)w->splits * w->m_tiles * 128 * cout;
+  return EQT_OK;
+}
+
+}  // namespace
+}  // namespace eqt
+
+extern "C" int64_t eqt_wgrad_tc_scratch_floats(int64_t n, int32_t cin, int32_t cout, const eqt_mix_block* blocks,
+                                               int32_t num_blocks) {
+  using namespace eqt;
+  if (n < 0 || cin <= 0 || cout <= 0 || cin % 32 || cout % 32 || num_blocks < 0 || (num_blocks && !blocks)) return -1;
+  int64_t need = 0;
+  for (int b = 0; b < num_blocks; ++b) {
+    WgradShape w{};
+    if (wgrad_shape(blocks[b], b, std::max<int64_t>(n, 1), cin, cout, &w)) return -1;
+    need = std::max(need, w.need);
+  }
+  return need;
+}
+
 extern "C" int eqt_wgrad_tc(const float* s, const float* g, float* gw_packed, float* scratch, int64_t scratch_floats,
                             int64_t n, int32_t rows, int32_t comps, int32_t cin, int32_t cout,
                             const eqt_mix_block* blocks, int32_t num_blocks, int32_t* status, void* stream) {
@@ -226,37 +259,30 @@ extern "C" int eqt_wgrad_tc(const float* s, const float* g, float* gw_packed, fl
   if (cin % 32 != 0 || cout % 32 != 0 || cout > 128)
     return fail(EQT_ERR_UNSUPPORTED, "tensor-core weight gradient needs C_in %% 32 == 0, C_out %% 32 == 0, C_out <= 128");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  static bool configured = false;
-  if (!configured) {
+  {
     cudaError_t e = cudaFuncSetAttribute(wgrad_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
     if (e != cudaSuccess) return fail(EQT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    configured = true;
   }
-  const int b_boxes = cout / 32;
-  const size_t budget = 220 * 1024 - 1024;
+  // every block is checked before the first launch, so a refusal leaves gw_packed untouched
+  std::vector<WgradShape> shapes(num_blocks);
+  for (int b = 0; b < num_blocks; ++b) {
+    if (int rc = wgrad_shape(blocks[b], b, n, cin, cout, &shapes[b])) return rc;
+    if (shapes[b].need > scratch_floats)
+      return fail(EQT_ERR_BAD_ARGUMENT, "scratch too small: block %d needs %lld floats, %lld given", b,
+                  (long long)shapes[b].need, (long long)scratch_floats);
+  }
   for (int b = 0; b < num_blocks; ++b) {
     const eqt_mix_block& blk = blocks[b];
-    if (blk.dim <= 0 || blk.dim > TILE_M || blk.paths <= 0) return fail(EQT_ERR_BAD_ARGUMENT, "bad block %d", b);
-    const int64_t K = (int64_t)blk.paths * cin;                 // M extent of this GEMM
-    const int m_tiles = (int)ceil_div(K, 128);
-    // reduction rows per tile: multiple of 8 and of dim, two stages must fit in shared memory
-    const size_t bytes_per_row = 2 * (size_t)(4 + b_boxes) * 128;
-    int rows_cap = (int)std::min<size_t>(128, budget / 2 / bytes_per_row);
-    int step = 8;
-    for (int d = blk.dim; d % 2 == 0 && step > 1; d /= 2) step /= 2;   // 8 / gcd(dim, 8)
-    const int npt = (rows_cap / blk.dim) / step * step;
-    if (npt <= 0) return fail(EQT_ERR_UNSUPPORTED, "irrep with %d components does not fit a reduction tile", blk.dim);
+    const WgradShape& w = shapes[b];
+    const int64_t K = w.K;
+    const int m_tiles = w.m_tiles, npt = w.npt, splits = w.splits;
+    const size_t stage_bytes = w.stage_bytes;
     WgradArgs a{};
     a.n = n; a.dim = blk.dim; a.npt = npt; a.n_cols = cout; a.status = status;
-    const size_t stage_bytes = bytes_per_row * (size_t)(npt * blk.dim);
-    a.stages = (int)std::min<size_t>(4, budget / stage_bytes);
+    a.stages = w.stages;
     a.tmem_cols = 32;
     while (a.tmem_cols < 2 * cout) a.tmem_cols <<= 1;
-    a.chunk_tiles = std::max(1, 512 / (npt * blk.dim));
-    const int64_t tiles = ceil_div(n, npt);
-    const int splits = (int)std::max<int64_t>(1, std::min<int64_t>(tiles, sm_count() / m_tiles));
-    const int64_t need = (int64_t)splits * m_tiles * 128 * cout;
-    if (need > scratch_floats) return fail(EQT_ERR_BAD_ARGUMENT, "scratch too small: %lld floats needed", (long long)need);
+    a.chunk_tiles = w.chunk_tiles;
     a.partial = scratch;
     CUtensorMap map_s, map_g;
     {
@@ -335,6 +361,17 @@ extern "C" int eqt_wgrad_tc_static(const float* s, const float* g, float* gw_pac
                 "eqt_wgrad_tc_static: %d SMs x 128 x %d floats exceed the built-in scratch of %lld floats; use "
                 "eqt_wgrad_tc with a caller-provided scratch buffer", sm_count(), (int)cout,
                 (long long)kStaticScratchFloats);
+  if (n > 0 && num_blocks > 0 && blocks && cin > 0 && cin % 32 == 0 && cout > 0 && cout % 32 == 0) {
+    for (int b = 0; b < num_blocks; ++b) {   // the real need of every block, before anything is launched
+      WgradShape w{};
+      if (int rc = wgrad_shape(blocks[b], b, n, cin, cout, &w)) return rc;
+      if (w.need > kStaticScratchFloats)
+        return fail(EQT_ERR_UNSUPPORTED,
+                    "eqt_wgrad_tc_static: block %d (%d paths x %d input channels) needs %lld floats of scratch, the "
+                    "built-in scratch holds %lld; use eqt_wgrad_tc with a caller-provided scratch buffer", b,
+                    (int)blocks[b].paths, (int)cin, (long long)w.need, (long long)kStaticScratchFloats);
+    }
+  }
   float* scratch = nullptr;
   if (int rc = static_scratch(&scratch)) return rc;
   return eqt_wgrad_tc(s, g, gw_packed, scratch, kStaticScratchFloats, n, rows, comps, cin, cout, blocks, num_blocks,

@@ -200,7 +200,7 @@ int sh_launch_unrolled(bool backward, const void* xyz, const void* gout, void* o
                        cudaStream_t s) {
   using A = typename Acc<T>::type;
   constexpr int K = (LMAX + 1) * (LMAX + 1);
-  const unsigned grid = flat_grid(n, 256, 148 * 8);
+  const unsigned grid = flat_grid(n, 256, 8);
   if (backward) {
     sh_backward_unrolled_kernel<T, LMAX><<<grid, 256, 0, s>>>(static_cast<const T*>(xyz), static_cast<const T*>(gout),
                                                               static_cast<T*>(out), n, normalize, (A)out_scale);
@@ -265,7 +265,7 @@ int sh_launch(bool backward, const void* xyz, const void* gout, void* out, int64
   int threads = 256;
   while (threads > 32 && per_thread * threads > 64 * 1024) threads >>= 1;
   const size_t bytes = per_thread * threads;
-  const unsigned grid = flat_grid(n, threads, 148 * 8);
+  const unsigned grid = flat_grid(n, threads, 8);
   if (backward) {
     if (int rc = configure_smem(sh_backward_kernel<T>, bytes)) return rc;
     sh_backward_kernel<T><<<grid, threads, bytes, s>>>(static_cast<const T*>(xyz), static_cast<const T*>(gout),

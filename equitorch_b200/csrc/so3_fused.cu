@@ -498,12 +498,9 @@ template <class S, int CPL, int CG>
 int launch_spec(bool inner, const FusedArgs& a, cudaStream_t s) {
   constexpr size_t bytes = Smem<S, CPL, CG>::bytes();
   auto kern = inner ? tp_inner_spec_kernel<S, CPL, CG> : tp_segsum_spec_kernel<S, CPL, CG>;
-  static bool configured[2] = {false, false};
-  if (!configured[inner]) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-    if (e != cudaSuccess) return fail(EQT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    configured[inner] = true;
-  }
+  // the attribute belongs to the current device's context, so it is set on every launch (a cheap host-side call)
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e != cudaSuccess) return fail(EQT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   const unsigned grid = (unsigned)ceil_div(a.n_out, a.nodes_per_cta);
   kern<<<grid, 128 * CG, bytes, s>>>(a);
   return check_launch(inner ? "tp_inner_spec_kernel" : "tp_segsum_spec_kernel");
@@ -522,7 +519,7 @@ int run(bool inner, const eqt_tp_table* tab, FusedArgs a, cudaStream_t s) {
   if (a.n_out == 0 || (inner && a.n_edges == 0)) return EQT_OK;
   if ((reinterpret_cast<uintptr_t>(a.feat) & 15u) == 0 && a.status && a.scale_o && (!inner || a.ptr) && a.n_edges < 0x7fffffffll) {
     // nodes per CTA: keep every SM busy with several CTAs but amortise the pipeline prologue
-    int64_t per = std::max<int64_t>(1, a.n_out / (148 * 16));
+    int64_t per = std::max<int64_t>(1, a.n_out / ((int64_t)sm_count() * 16));
     const int64_t avg_deg = std::max<int64_t>(1, a.n_edges / std::max<int64_t>(1, a.n_out));
     per = std::min<int64_t>(per, std::max<int64_t>(1, 256 / avg_deg));
     a.nodes_per_cta = (int)per;
@@ -535,7 +532,7 @@ int run(bool inner, const eqt_tp_table* tab, FusedArgs a, cudaStream_t s) {
     if (!a.enode) return fail(EQT_ERR_BAD_ARGUMENT, "edge_node is required by the table-driven kernel");
     const size_t bytes = sizeof(float) * 4 * a.DY * 32;
     if (bytes > 48 * 1024) return fail(EQT_ERR_UNSUPPORTED, "d_y = %d is too large for the table-driven kernel", a.DY);
-    tp_inner_generic_kernel<<<flat_grid(a.n_edges, 4, 148 * 16), 128, bytes, s>>>(a);
+    tp_inner_generic_kernel<<<flat_grid(a.n_edges, 4, 16), 128, bytes, s>>>(a);
     return check_launch("tp_inner_generic_kernel");
   }
   tp_segsum_generic_kernel<<<flat_grid(a.n_out * a.R * a.C, 256), 256, 0, s>>>(a);

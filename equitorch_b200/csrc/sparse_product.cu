@@ -23,6 +23,20 @@ int fail(int code, const char* fmt, ...) {
   va_end(ap);
   return code;
 }
+int sm_count() {
+  constexpr int kMaxDevices = 64;
+  static std::atomic<int> cached[kMaxDevices];   // zero-initialised; a race only repeats the query
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (dev >= 0 && dev < kMaxDevices) {
+    const int n = cached[dev].load(std::memory_order_relaxed);
+    if (n > 0) return n;
+  }
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  if (dev >= 0 && dev < kMaxDevices) cached[dev].store(n, std::memory_order_relaxed);
+  return n;
+}
 
 namespace {
 
@@ -411,7 +425,7 @@ int launch(const eqt_product_args& a, P p, cudaStream_t s) {
     if (p.c1 == 0) return EQT_OK;
     if (a.accumulated) {
       const int64_t blocks_x = p.num_out * ceil_div(p.c1, 32);
-      int64_t chunks = ceil_div(148 * 8, blocks_x);
+      int64_t chunks = ceil_div((int64_t)sm_count() * 8, blocks_x);
       chunks = std::max<int64_t>(1, std::min<int64_t>(chunks, ceil_div(p.n, 64)));
       chunks = std::min<int64_t>(chunks, 65535);
       const int64_t chunk = ceil_div(p.n, chunks);
@@ -440,7 +454,7 @@ int launch(const eqt_product_args& a, P p, cudaStream_t s) {
     if (a.accumulated) {
       const int64_t tiles = ceil_div(p.c1, 64) * ceil_div(p.c2, 64);
       if (p.num_out > 65535) return fail(EQT_ERR_UNSUPPORTED, "accumulated outer: more than 65535 output rows");
-      int64_t chunks = ceil_div(148 * 4, tiles * p.num_out);
+      int64_t chunks = ceil_div((int64_t)sm_count() * 4, tiles * p.num_out);
       chunks = std::max<int64_t>(1, std::min<int64_t>(chunks, ceil_div(p.n, 32)));
       chunks = std::min<int64_t>(chunks, 65535);
       const int64_t chunk = ceil_div(p.n, chunks);

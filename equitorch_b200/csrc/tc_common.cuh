@@ -164,16 +164,7 @@ inline int make_map(CUtensorMap* map, const float* base, int rank, const cuuint6
   return EQT_OK;
 }
 
-inline int sm_count() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
-}
+using ::eqt::sm_count;   // per-device SM count (common.cuh)
 
 }  // namespace tc
 }  // namespace eqt

@@ -20,6 +20,7 @@ No per-edge tensor with a channel axis is ever written to memory.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -29,10 +30,17 @@ from torch.autograd import Function
 from ... import _profile
 from ...graph import EdgeGraph
 from ...ops import batched_sparse_dense_op as _ops
-from ...ops.fused_tp_op import TpTable, cg_inner, cg_segment_sum
+from ...ops.fused_tp_op import TpTable, cg_inner, cg_segment_sum, check_status
 from ...ops.mix_tc_op import (MixPlan, mix_tc, mix_tc_transposed, wgrad_tc, supported as _tc_supported,
                               supported_transposed as _tc_supported_t, supported_wgrad as _tc_supported_w)
 from ...structs import TensorProductInfo
+
+
+# The fused kernels bound every wait on an asynchronous copy; a wait that runs out raises a per-device status
+# word and the kernel returns with partial output.  `fused_tp_op.check_status()` turns the word into an
+# exception (it synchronises, so it is not called on the hot path); EQT_CHECK_STATUS=1 makes every forward and
+# backward of the fused layer call it.
+_CHECK_EVERY_CALL = os.environ.get("EQT_CHECK_STATUS", "0") not in ("", "0")
 
 
 class GraphTPPlan:
@@ -71,6 +79,8 @@ class SO3LinearGraphFunction(Function):
             out = _mix(s, weight, plan.mix_fwd, mode, plan.tc_fwd)
         ctx.save_for_backward(node_x, y, weight, s if weight.requires_grad else None)
         ctx.graph, ctx.plan, ctx.mode = graph, plan, mode
+        if _CHECK_EVERY_CALL:
+            check_status(node_x.device)
         return out
 
     @staticmethod
@@ -117,6 +127,8 @@ class SO3LinearGraphFunction(Function):
                                     graph.num_src)
             with _profile.timed("channel_mix[grad_x]"):
                 gx = _mix(sx, wt, plan.mix_src, mode, plan.tc_src)
+        if _CHECK_EVERY_CALL:
+            check_status(grad.device)
         return gx, gy, gw, None, None, None
 
 

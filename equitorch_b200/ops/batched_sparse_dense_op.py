@@ -82,8 +82,15 @@ def sparse_product(op: int, input1: Tensor, input2: Optional[Tensor], scale=None
         if op == _lib.OP_VECMAT and y.shape[-2] != c1:
             raise ValueError(f"vector has {c1} channels, matrix expects {y.shape[-2]}")
     if n1 is not None and n2 is not None and n1 != n2:
-        raise ValueError(f"batch sizes differ: {n1} vs {n2}")
-    n = n1 if n1 is not None else (n2 if n2 is not None else 1)
+        # N = max of the two batch sizes as in the reference (:189); the only well-defined unequal case is a
+        # batch of one, which is the shared operand with an explicit leading 1
+        if n1 == 1:
+            x, shared1, n1 = x[0], True, None
+        elif n2 == 1:
+            y, shared2, n2 = y[0], True, None
+        else:
+            raise ValueError(f"batch sizes differ: {n1} vs {n2}")
+    n = max(n1 or 1, n2 or 1)
 
     index1 = _index(index1, "index1", dev)
     index2 = _index(index2, "index2", dev)
@@ -108,10 +115,17 @@ def sparse_product(op: int, input1: Tensor, input2: Optional[Tensor], scale=None
     lead = (out_size,) if out_accumulated else (n, out_size)
     work_dtype = arith if out_accumulated else rt
     must_zero = out_accumulated or index_out is not None or out_size != num_out
-    if out is not None and out.is_contiguous() and out.dtype == work_dtype and tuple(out.shape) == (*lead, *tail):
-        buf = out
+    if out is not None:
+        # the reference writes into `out`; a buffer the kernels cannot write into is an error, not a silent copy
+        if tuple(out.shape) != (*lead, *tail) or out.dtype != rt or out.device != dev or not out.is_contiguous():
+            raise ValueError(f"out must be a contiguous {rt} tensor of shape {(*lead, *tail)} on {dev}, got "
+                             f"{out.dtype} {tuple(out.shape)} on {out.device} (contiguous: {out.is_contiguous()})")
+    if out is not None and out.dtype == work_dtype:
+        buf = out          # accumulated / indexed outputs add into the caller's values, as in the reference
     else:
         buf = (torch.zeros if must_zero else torch.empty)((*lead, *tail), dtype=work_dtype, device=dev)
+        if out is not None and must_zero:
+            buf.copy_(out)     # bfloat16 `out` summed in float32: start from the caller's values
 
     args = _lib.ProductArgs(
         op=op, dtype=_lib.DTYPE_CODE[rt], shared1=int(shared1), shared2=int(shared2),
@@ -122,6 +136,9 @@ def sparse_product(op: int, input1: Tensor, input2: Optional[Tensor], scale=None
         n=n, rows1=rows1, rows2=rows2, num_out=num_out, out_size=out_size, c1=c1, c2=c2)
     with torch.cuda.device(dev):
         _lib.check(_lib.lib().eqt_sparse_product(C.byref(args), _lib.stream_ptr(dev)), "eqt_sparse_product")
+    if out is not None and buf is not out:
+        out.copy_(buf)
+        return out
     return buf if buf.dtype == rt else buf.to(rt)
 
 

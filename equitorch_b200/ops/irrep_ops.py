@@ -13,8 +13,8 @@ PER_SAMPLE_CHANNEL, SHARED, PER_SAMPLE = 0, 1, 2
 def _check(x: Tensor) -> None:
     if x.ndim != 3:
         raise ValueError(f"features must be (N, components, channels), got {tuple(x.shape)}")
-    if x.dtype not in (torch.float32, torch.float64):
-        raise TypeError(f"float32 or float64 features expected, got {x.dtype}")
+    if x.dtype not in (torch.float32, torch.float64, torch.bfloat16):
+        raise TypeError(f"float32, float64 or bfloat16 features expected, got {x.dtype}")
 
 
 def irrep_scale(x: Tensor, s: Tensor, irrep_index: Tensor, mode: int) -> Tensor:

@@ -98,11 +98,11 @@ def mix_tc_transposed(g: Tensor, weight: Tensor, plan: MixPlan) -> Tensor:
 _scratch = {}
 
 
-def wgrad_scratch(device, cout: int) -> Tensor:
-    """Per-device scratch for the split reduction of :func:`wgrad_tc` (128 * cout floats per SM)."""
+def wgrad_scratch(device, cout: int, need: int = 0) -> Tensor:
+    """Per-device scratch for the split reduction of :func:`wgrad_tc` (at least 128 * cout floats per SM)."""
     device = torch.device(device)
     sms = torch.cuda.get_device_properties(device).multi_processor_count
-    need = 128 * cout * sms
+    need = max(need, 128 * cout * sms)
     buf = _scratch.get(device)
     if buf is None or buf.numel() < need:
         buf = torch.empty(need, dtype=torch.float32, device=device)
@@ -118,9 +118,12 @@ def wgrad_tc(s: Tensor, g: Tensor, plan: MixPlan, num_paths: int) -> Tensor:
     n, rows, cin = s.shape
     cout = g.shape[-1]
     packed = torch.empty(plan.path_gather.numel(), cin, cout, dtype=torch.float32, device=dev)
-    scratch = wgrad_scratch(dev, cout)
     blocks = plan.structs(cin, cout)
     with torch.cuda.device(dev):
+        need = int(_lib.lib().eqt_wgrad_tc_scratch_floats(n, cin, cout, blocks, len(blocks)))
+        if need < 0:
+            raise _lib.EqtError("eqt_wgrad_tc refuses these blocks")
+        scratch = wgrad_scratch(dev, cout, need)
         _lib.check(_lib.lib().eqt_wgrad_tc(s.data_ptr(), g.data_ptr(), packed.data_ptr(), scratch.data_ptr(),
                                            scratch.numel(), n, rows, plan.comps, cin, cout, blocks, len(blocks),
                                            status_flag(dev).data_ptr(), _lib.stream_ptr(dev)), "eqt_wgrad_tc")

@@ -104,3 +104,36 @@ def test_layer_rms_unfused_composition(key, monkeypatch):
     out, grads, _ = run_case(key, case, _impl(key.split("/")[0], torch.float64))
     assert float((out.detach() - case["out"]).abs().max()) <= 1e-11
     assert float((grads[0] - case["gx"]).abs().max()) <= 1e-11 * max(1.0, float(case["gx"].abs().max()))
+
+
+def test_bfloat16_layers_against_oracle():
+    """bfloat16 features (the molecular configuration's dtype) run through the same layers: bfloat16 storage,
+    float32 arithmetic.  Checked against the float64 oracle on the bfloat16-rounded inputs at the 2e-2 the
+    tensor products use for bfloat16 (error = max |a - b| / max |b|)."""
+    name, n, c = "4x0e+2x1o+2e", 512, 32
+    ir = Irreps(name)
+    dims = [i.dim for i in ir]
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(n, ir.dim, c, generator=g).bfloat16()
+    gates = torch.randn(n, len(ir), c, generator=g).bfloat16()
+    w = (torch.rand(len(ir), c, generator=g) + 0.5).bfloat16()
+    cot = torch.randn(n, ir.dim, c, generator=g).bfloat16()
+
+    xo, go, wo = (t.double().requires_grad_(True) for t in (x, gates, w))
+    ref = ong.layer_rms_norm(ong.gate(xo, go, dims, torch.sigmoid), dims, wo, True, 1e-5)
+    gref = torch.autograd.grad(ref, [xo, go, wo], cot.double())
+    nref = ong.squared_norm(xo, dims, True)
+
+    gate = enn.Gate(ir, activation=torch.nn.Sigmoid()).to(DEV)
+    ln = enn.LayerRMSNorm(ir, c).to(DEV).to(torch.bfloat16)
+    xg, gg = (t.to(DEV).requires_grad_(True) for t in (x, gates))
+    ln.weight = torch.nn.Parameter(w.to(DEV))
+    out = ln(gate(xg, gg))
+    assert out.dtype == torch.bfloat16
+    grads = torch.autograd.grad(out, [xg, gg, ln.weight], cot.to(DEV))
+    info = irreps_info(ir).to(DEV)
+    got_norm = F.squared_norm(xg.detach(), info, True)
+    for a, b in zip([out, *grads, got_norm], [ref, *gref, nref]):
+        assert a.dtype == torch.bfloat16
+        err = float((a.detach().double().cpu() - b.detach()).abs().max() / b.detach().abs().max())
+        assert err < 2e-2, err
