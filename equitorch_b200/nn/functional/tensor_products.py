@@ -13,6 +13,7 @@ from torch import Tensor
 from torch.autograd import Function
 
 from ...structs import IrrepsInfo, SparseProductInfo, TensorProductInfo
+from ._irrep import irrep_dot
 from ._tp_common import add, expand_like_inter, save_for_tp_backward
 from .linears import _m, _mij, _rot
 from .sparse_product import sparse_mat_t_vec, sparse_mul, sparse_outer, sparse_vecmat
@@ -98,7 +99,8 @@ def tensor_product_uvw(input1, input2, weight, tp_info_forward, tp_info_backward
 
 
 class TensorDotUU(Function):
-    """Per-irrep dot product over the components: (N, D, C) x (N, D, C) -> (N, num_irreps, C)."""
+    """Per-irrep dot product on the table-driven sparse products (operands of different shape, e.g. one of them
+    shared by the batch)."""
 
     @staticmethod
     def forward(ctx, input1: Tensor, input2: Tensor, irreps_info: IrrepsInfo, scaled: bool = True):
@@ -123,7 +125,17 @@ class TensorDotUU(Function):
         return g1, g2, None, None
 
 
-tensor_dot_uu = TensorDotUU.apply
+def tensor_dot_uu(input1: Tensor, input2: Tensor, irreps_info: IrrepsInfo, scaled: bool = True) -> Tensor:
+    """Per-irrep dot product over the components, (N, D, C) x (N, D, C) -> (N, num_irreps, C), divided by
+    sqrt(2l + 1) when ``scaled`` (``TensorDotUU``, equitorch/nn/functional/tensor_products.py:173-223).  Operands of
+    equal shape and dtype take one pass of the streaming per-irrep dot kernel, whose gradients are the per-irrep
+    scale kernel (``_irrep.IrrepDot``)."""
+    if input1.shape != input2.shape or input1.dtype != input2.dtype or input1.ndim != 3:
+        return TensorDotUU.apply(input1, input2, irreps_info, scaled)
+    ret = irrep_dot(input1, input2, irreps_info)
+    if scaled:
+        ret = ret * irreps_info.rsqrt_dims.to(ret.dtype).unsqueeze(-1)
+    return ret
 
 
 def tensor_dot_uv(input1, input2, irreps_info, scaled=True):

@@ -143,3 +143,15 @@ def so3_linear_message_passing(node_x: Tensor, edge_vec: Tensor, src: Tensor, ds
                            feature_mode=feature_mode, **kw)
     n_out = node_x.shape[0] if num_out_nodes is None else num_out_nodes
     return msg.new_zeros(n_out, *msg.shape[1:]).index_add(0, dst, msg)
+
+
+def tensor_dot_uu(x1: Tensor, x2: Tensor, irreps, scaled: bool = True) -> Tensor:
+    """Irrep-wise dot product of two channelled features, (N, D, C) x (N, D, C) -> (N, num_irreps, C); with
+    ``scaled`` each irrep's sum is divided by sqrt(2l + 1) (equitorch/nn/functional/tensor_products.py:173-223,
+    module equitorch/nn/tensor_products.py:199-269)."""
+    ir = check_irreps(irreps)
+    outs = []
+    for (lo, hi) in _blocks(ir):
+        d = (x1[:, lo:hi] * x2[:, lo:hi]).sum(dim=1)
+        outs.append(d / (hi - lo) ** 0.5 if scaled else d)
+    return torch.stack(outs, dim=1)

@@ -110,3 +110,40 @@ def test_large_graph_properties():
     o1s = layer(x1, y[perm], shuffled)
     check_status()
     torch.testing.assert_close(o1s, o1, rtol=1e-4, atol=1e-4)
+
+
+def test_profiling_size_graph_prefix_against_oracle():
+    """The quarter-size benchmark graph (25k nodes, ~500k edges, l_max 3, C 64, uv) through the fused layer, output
+    and all three gradients against the float64 oracle on the first ~32k destination-contiguous edges - the slice
+    the CPU baseline of the benchmark times.  The cotangent is zero outside the prefix nodes, so every gradient
+    depends on the prefix edges only.  Error = max |a - b| / max |b|, bound 1e-5."""
+    from equitorch_b200.utils.synthetic import node_features, radius_graph
+    ir, c = "0e+1o+2e+3o", 64
+    graph, _ = radius_graph(25_000, 500_000, seed=0)
+    nodes, edges = graph.num_nodes, graph.src.numel()
+    n_pre = 32768
+    last = int(graph.dst[n_pre - 1])
+    n_pre = int(torch.searchsorted(graph.dst, torch.tensor(last), right=True))
+    g = torch.Generator().manual_seed(4)
+    x = node_features(nodes, 16, c, seed=1)
+    w = (torch.rand(23, c, c, generator=g) * 2 - 1) * (3.0 / c) ** 0.5
+    cot = torch.randn(nodes, 16, c, generator=g)
+    cot[last + 1:] = 0
+
+    layer = enn.SO3LinearGraph(ir, ir, ir, c, c, internal_weights=False, feature_mode="uv").to(DEV)
+    eg = EdgeGraph(graph.src.to(DEV), graph.dst.to(DEV), nodes)
+    xg, vg, wg = (t.to(DEV).requires_grad_(True) for t in (x, graph.edge_vec, w))
+    out = layer(xg, enn.SphericalHarmonics(3)(vg), eg, wg)
+    gx, gv, gw = torch.autograd.grad(out, [xg, vg, wg], cot.to(DEV))
+    check_status()
+
+    xo, wo = x.double().requires_grad_(True), w.double().requires_grad_(True)
+    vo = graph.edge_vec[:n_pre].double().requires_grad_(True)
+    ref = otp.so3_linear_message_passing(xo, vo, graph.src[:n_pre], graph.dst[:n_pre], wo, ir, ir, ir, feature_mode="uv",
+                                         num_out_nodes=last + 1)
+    rx, rv, rw = torch.autograd.grad(ref, [xo, vo, wo], cot[: last + 1].double())
+    assert torch.count_nonzero(gv[n_pre:]) == 0          # edges into nodes with a zero cotangent
+    pairs = [("out", out[: last + 1], ref), ("grad_x", gx, rx), ("grad_vec", gv[:n_pre], rv), ("grad_w", gw, rw)]
+    for name, a, b in pairs:
+        err = float((a.detach().double().cpu() - b.detach()).abs().max() / b.detach().abs().max())
+        assert err < 1e-5, f"{name}: relative error {err:.2e}"
