@@ -1,8 +1,8 @@
 """Benchmark of the hot path: edges/s of the Clebsch-Gordan tensor-product layer, forward + backward
 (l_max = 3, 64 channels, full 64 -> 64 channel mixing per path), on N GPUs of one box.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg5|cfg5q|cfg2|epilogue] [--impl ours|reference]
-                    [--no-graph] [--no-cpu-baseline]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg5|cfg5q|cfg2|cfg1|cfg3|cfg4|epilogue]
+                    [--feature-mode uv|uu] [--repeats R] [--impl ours|reference] [--no-graph] [--no-cpu-baseline]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
 One step = one pass of the layer over one synthetic graph: spherical harmonics of the edge vectors,
@@ -16,7 +16,11 @@ Workloads (seeded synthetic data, shapes of the benchmark configurations):
         intermediates) is far larger than the 126 MB L2, so no explicit flush is needed.
   cfg5q a quarter-size cfg5 (25k nodes, ~500k edges) for profiler captures.
   cfg2  200k edges with uniformly random sources over 10k nodes (single GPU).  Its node table fits in
-        L2, so L2 is flushed between steps and every step is timed on its own.
+        L2, so L2 is flushed between steps and every step is timed on its own.  ``--feature-mode uu`` runs the
+        same graph with per-path channel-wise weights (23 x 64) instead of the 64 x 64 mixing.
+  cfg1 / cfg3 / cfg4  the small configurations (equitorch_b200/utils/workloads.py), one GPU, their own JSON
+        lines: per-sample 'uu' product at l_max 2; molecular-style layer with per-edge bfloat16 weights;
+        Wigner-rotated SO(2) linear layer at l = 0..6.  L2 is flushed between steps.
   epilogue  side measurement, one GPU: Gate -> BatchRMSNorm -> LayerRMSNorm forward + backward on 100k x 16 x 64
         node features (its own JSON line; not the metric of the benchmark).
 
@@ -52,7 +56,7 @@ METRIC = "edges/s, CG tensor product fwd+bwd (lmax=3, C=64)"
 
 
 # ----------------------------------------------------------------------------------------------
-def make_workload(name: str):
+def make_workload(name: str, mode: str = "uv"):
     from equitorch_b200.utils.synthetic import node_features, radius_graph, random_graph
     if name == "cfg5":
         graph, _ = radius_graph(100_000, 2_000_000, seed=0)
@@ -68,7 +72,10 @@ def make_workload(name: str):
     x = node_features(graph.num_nodes, DIM, CHANNELS, seed=1)
     gen = torch.Generator().manual_seed(2)
     cot = torch.randn(graph.num_nodes, DIM, CHANNELS, generator=gen)
-    weight = (torch.rand(PATHS, CHANNELS, CHANNELS, generator=gen) * 2 - 1) * (3.0 / CHANNELS) ** 0.5
+    if mode == "uv":
+        weight = (torch.rand(PATHS, CHANNELS, CHANNELS, generator=gen) * 2 - 1) * (3.0 / CHANNELS) ** 0.5
+    else:
+        weight = (torch.rand(PATHS, CHANNELS, generator=gen) * 2 - 1) * 3.0 ** 0.5
     return graph, x, cot, weight, label
 
 
@@ -125,58 +132,134 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------------------------
-# CPU arm: the oracle (a CPU port of the reference's algorithm) on a bounded sample of the workload
+# CPU arm.  Two timings on the host cores, both on bounded, destination-contiguous samples of the workload:
+#   "reference": the reference package itself (installed unmodified under baseline/_ref by build(); its two
+#                torch_geometric reductions come from the documented-semantics stand-in of
+#                tests/golden/_reference_import.py) - gather, SphericalHarmonics, SO3Linear, index_add, backward -
+#                in chunks of 1024 edges, because its CPU path materialises ~1.6 MB of scratch per edge;
+#   "port":      the oracle (oracle/, a dense-einsum restatement of the same algorithm) on ~32k edges.
 # ----------------------------------------------------------------------------------------------
-def cpu_sample_step(graph, x, cot, weight, max_edges: int):
-    """Forward + backward of the oracle on the first destination nodes holding ~max_edges edges."""
-    from oracle import tensor_products as otp
-    n_edges = min(max_edges, graph.src.numel())
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+
+
+def _prefix(graph, n_edges):
+    n_edges = min(n_edges, graph.src.numel())
     last_node = int(graph.dst[n_edges - 1])
     n_edges = int(torch.searchsorted(graph.dst, torch.tensor(last_node), right=True))
+    return n_edges, last_node
+
+
+def cpu_sample_step(graph, x, cot, weight, max_edges: int, mode: str = "uv"):
+    """Forward + backward of the oracle on the first destination nodes holding ~max_edges edges."""
+    from oracle import tensor_products as otp
+    n_edges, last_node = _prefix(graph, max_edges)
     src, dst, vec = graph.src[:n_edges], graph.dst[:n_edges], graph.edge_vec[:n_edges]
     xs = x.clone().requires_grad_(True)
     vs = vec.clone().requires_grad_(True)
     ws = weight.clone().requires_grad_(True)
     t0 = time.perf_counter()
-    out = otp.so3_linear_message_passing(xs, vs, src, dst, ws, IRREPS, IRREPS, IRREPS, feature_mode="uv",
+    out = otp.so3_linear_message_passing(xs, vs, src, dst, ws, IRREPS, IRREPS, IRREPS, feature_mode=mode,
                                          num_out_nodes=last_node + 1)
     torch.autograd.grad(out, [xs, vs, ws], cot[: last_node + 1])
     return n_edges, time.perf_counter() - t0
 
 
-def cpu_baseline(graph, x, cot, weight, max_edges=32768, repeats=2):
+_reference_layer = {}
+
+
+def reference_available() -> bool:
+    return os.path.isdir(os.path.join(REF_DIR, "equitorch"))
+
+
+def reference_chunk_step(graph, x, cot, weight, first_edge: int, chunk: int = 1024, mode: str = "uv"):
+    """One chunk of `chunk` edges through the reference's own modules on the CPU: forward + backward."""
+    os.environ["EQUITORCH_REFERENCE_ROOT"] = REF_DIR
+    from tests.golden._reference_import import import_reference
+    import_reference()
+    from equitorch.nn.linears import SO3Linear as RefSO3Linear
+    from equitorch.nn.sphericals import SphericalHarmonics as RefSH
+    if mode not in _reference_layer:
+        _reference_layer[mode] = (RefSO3Linear(IRREPS, IRREPS, IRREPS, CHANNELS, CHANNELS, internal_weights=False,
+                                               feature_mode=mode), RefSH(L_MAX))
+    layer, sh = _reference_layer[mode]
+    e0, e1 = first_edge, min(first_edge + chunk, graph.src.numel())
+    src, dst, vec = graph.src[e0:e1], graph.dst[e0:e1], graph.edge_vec[e0:e1]
+    d0, d1 = int(dst[0]), int(dst[-1]) + 1
+    xs = x.clone().requires_grad_(True)
+    vs = vec.clone().requires_grad_(True)
+    ws = weight.clone().requires_grad_(True)           # the reference's backward needs a weight that requires grad
+    t0 = time.perf_counter()
+    msg = layer(xs[src], sh(vs), ws)
+    out = torch.zeros(d1 - d0, DIM, CHANNELS).index_add(0, dst - d0, msg)
+    torch.autograd.grad(out, [xs, vs, ws], cot[d0:d1])
+    return e1 - e0, time.perf_counter() - t0
+
+
+def cpu_baseline(graph, x, cot, weight, mode="uv", max_edges=32768, repeats=2, chunks=5):
     torch.set_num_threads(os.cpu_count() or 1)
     best, n_edges = None, 0
     for _ in range(repeats + 1):              # first run warms up the allocator and thread pool
-        n_edges, dt = cpu_sample_step(graph, x, cot, weight, max_edges)
+        n_edges, dt = cpu_sample_step(graph, x, cot, weight, max_edges, mode)
         best = dt if best is None else min(best, dt)
-    return {"value": n_edges / best, "unit": "edges/s", "cores": torch.get_num_threads(), "kind": "port",
+    port = {"value": n_edges / best, "unit": "edges/s", "cores": torch.get_num_threads(), "kind": "port",
             "sample": f"first {n_edges} edges (by destination) of the workload, fwd+bwd, float32, best of {repeats}"}
+    if not reference_available():
+        port["reference_unavailable"] = "baseline/_ref is absent (build() installs it where the reference checkout exists)"
+        return port
+    reference_chunk_step(graph, x, cot, weight, 0, mode=mode)            # warm-up chunk
+    done, spent = 0, 0.0
+    for k in range(chunks):
+        n, dt = reference_chunk_step(graph, x, cot, weight, k * 1024, mode=mode)
+        done += n
+        spent += dt
+    return {"value": done / spent, "unit": "edges/s", "cores": torch.get_num_threads(), "kind": "reference",
+            "sample": f"{chunks} chunks of 1024 destination-contiguous edges through the reference's own SO3Linear / "
+                      "SphericalHarmonics on the CPU (gather + layer + index_add, fwd+bwd, float32), mean over chunks",
+            "port": port}
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    graph, x, cot, weight, label = make_workload(args.workload)
+    mode = args.feature_mode
+    graph, x, cot, weight, label = make_workload(args.workload if args.workload in ("cfg5", "cfg5q", "cfg2") else "cfg5", mode)
     torch.set_num_threads(os.cpu_count() or 1)
-    max_edges = 32768
-    for _ in range(args.warmup):
-        cpu_sample_step(graph, x, cot, weight, max_edges)
+    use_ref = reference_available()
+    chunks = 2          # ~5 s of CPU work per step on 8 cores
+
+    def one_step(k):
+        if not use_ref:
+            return cpu_sample_step(graph, x, cot, weight, 32768, mode)
+        n_tot, t_tot = 0, 0.0
+        for c in range(chunks):
+            n, dt = reference_chunk_step(graph, x, cot, weight, ((k * chunks + c) * 1024) % max(1, graph.src.numel() - 1024),
+                                         mode=mode)
+            n_tot += n
+            t_tot += dt
+        return n_tot, t_tot
+
+    for k in range(args.warmup):
+        one_step(k)
     total_edges, total_time = 0, 0.0
-    for _ in range(args.steps):
-        n, dt = cpu_sample_step(graph, x, cot, weight, max_edges)
+    for k in range(args.steps):
+        n, dt = one_step(k)
         total_edges += n
         total_time += dt
     value = total_edges / total_time
+    per_step = total_edges // max(1, args.steps)
+    kind = "reference" if use_ref else "port"
+    what = ("the reference package itself (baseline/_ref) on the CPU: gather + SphericalHarmonics + SO3Linear + index_add, "
+            f"fwd+bwd, {chunks} chunks of 1024 destination-contiguous edges per step" if use_ref else
+            "CPU port of the reference's algorithm (oracle/); baseline/_ref is absent")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "edges/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total_time / max(1, args.steps),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": label, "note": "CPU port of the reference's algorithm (oracle/), all host threads; "
-                   f"each step is a bounded sample of {total_edges // max(1, args.steps)} edges of the workload"},
-        "cpu_baseline": {"value": value, "unit": "edges/s", "cores": torch.get_num_threads(), "kind": "port",
-                         "sample": f"{total_edges // max(1, args.steps)} edges per step"},
+        "config": {"workload": label, "feature_mode": mode,
+                   "note": f"{what}; all host threads; each step is a bounded sample of {per_step} edges of the workload"},
+        "cpu_baseline": {"value": value, "unit": "edges/s", "cores": torch.get_num_threads(), "kind": kind,
+                         "sample": f"{per_step} edges per step"},
         "e2e": {"value": value, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))
@@ -229,12 +312,108 @@ def run_epilogue(args):
     }))
 
 
+def run_small(args):
+    """cfg1 / cfg3 / cfg4 on one GPU: the step of equitorch_b200/utils/workloads.py, L2 flushed between steps, every
+    step timed on its own with CUDA events; end to end with the inputs copied from pinned host memory and the
+    loss and gradients read back every step.  The roofline figure is the whole step against its minimal traffic."""
+    from equitorch_b200 import _lib
+    from equitorch_b200.utils.workloads import BUILDERS
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    wl = BUILDERS[args.workload](dev)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    for _ in range(max(args.warmup, 3)):
+        wl.step()
+    torch.cuda.synchronize(dev)
+    sampler = ClockSampler(0).start()
+    launches0 = _lib.launch_count()
+    per_repeat = []
+    for _ in range(max(1, args.repeats)):
+        pairs = []
+        for _ in range(args.steps):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            wl.step()
+            b.record()
+            pairs.append((a, b))
+        torch.cuda.synchronize(dev)
+        per_repeat.append(sum(a.elapsed_time(b) for a, b in pairs))
+    launches = (_lib.launch_count() - launches0) // max(1, args.repeats)
+    clocks = sampler.stop()
+    per_repeat.sort()
+    ms = per_repeat[len(per_repeat) // 2] / max(1, args.steps)
+
+    # the same steps replayed as a CUDA graph (these configurations are launch-bound from Python)
+    graph_ms, graph_error = None, None
+    if not args.no_graph:
+        try:
+            from equitorch_b200.utils.cuda_graph import GraphedStep
+            gs = GraphedStep(wl.step, dev, warmup=2)
+            for _ in range(3):
+                gs.replay()
+            pairs = []
+            for _ in range(args.steps):
+                flush.zero_()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                gs.replay()
+                b.record()
+                pairs.append((a, b))
+            torch.cuda.synchronize(dev)
+            graph_ms = sum(a.elapsed_time(b) for a, b in pairs) / max(1, args.steps)
+            del gs
+        except Exception as exc:  # noqa: BLE001
+            graph_error = f"{type(exc).__name__}: {exc}"[:300]
+            torch.cuda.synchronize(dev)
+
+    def e2e(count):
+        last = None
+        for _ in range(count):
+            with torch.no_grad():
+                for d, h in zip(wl.dev_inputs, wl.host_inputs):
+                    d.copy_(h, non_blocking=True)
+            loss, results = wl.step()
+            last = [loss.cpu()] + [r.cpu() for r in results[:1]]      # loss and the weight gradient
+        return last
+    e2e(2)
+    torch.cuda.synchronize(dev)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    last = e2e(args.steps)
+    t1.record()
+    torch.cuda.synchronize(dev)
+    e2e_ms = t0.elapsed_time(t1) / max(1, args.steps)
+    pk = peaks()
+    best_ms = min(ms, graph_ms) if graph_ms else ms
+    gbs = wl.algorithmic_bytes_per_unit * wl.units / (best_ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": f"{wl.unit}/s, {args.workload} fwd+bwd", "value": wl.units / (best_ms * 1e-3), "unit": f"{wl.unit}/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": best_ms, "eager_ms_per_step": ms,
+        "graph_ms_per_step": graph_ms, "cuda_graph_error": graph_error, "higher_is_better": True, "dtype": wl.dtype,
+        "data": "synthetic", "repeats": len(per_repeat),
+        "config": {"workload": wl.label, "l2": "256 MB written between steps to flush L2; steps timed individually"},
+        "e2e": {"value": wl.units / (e2e_ms * 1e-3), "unit": f"{wl.unit}/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": int(sum(h.numel() * h.element_size() for h in wl.host_inputs)),
+                "d2h_bytes_per_step": int(sum(t.numel() * t.element_size() for t in last)),
+                "copied_back": "loss and the weight gradient"},
+        "gpu_launches": int(launches), "clocks": clocks,
+        "roofline": {"kernel": "whole step", "bound": "hbm", "achieved": round(gbs, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(gbs / pk["hbm_gbs"], 4), "peak_source": pk["source"],
+                     "algorithmic_bytes_per_unit": wl.algorithmic_bytes_per_unit, "algorithmic_note": wl.note,
+                     "traffic": None},
+    }), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="cfg5", choices=["cfg5", "cfg2", "cfg5q", "epilogue"])
+    ap.add_argument("--workload", default="cfg5", choices=["cfg5", "cfg2", "cfg5q", "cfg1", "cfg3", "cfg4", "epilogue"])
+    ap.add_argument("--feature-mode", default="uv", choices=["uv", "uu"],
+                    help="uv: 64 x 64 channel mixing per path (the metric); uu: channel-wise weights per path")
+    ap.add_argument("--repeats", type=int, default=5, help="how often the timed region of K steps is repeated (median reported)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time the eager step only (no CUDA-graph replay)")
@@ -243,6 +422,8 @@ def main():
         return run_reference(args)
     if args.workload == "epilogue":
         return run_epilogue(args)
+    if args.workload in ("cfg1", "cfg3", "cfg4"):
+        return run_small(args)
 
     import torch.distributed as dist
     from equitorch_b200 import _lib, _profile
@@ -265,7 +446,8 @@ def main():
     if args.workload == "cfg2" and world > 1:
         raise SystemExit("cfg2 is the single-GPU microbenchmark")
 
-    graph, x_all, cot_all, weight, label = make_workload(args.workload)
+    mode = args.feature_mode
+    graph, x_all, cot_all, weight, label = make_workload(args.workload, mode)
     plan = plan_shards(graph.src, graph.dst, graph.num_nodes, world)[rank]
     lo, hi, e0, e1 = plan.node_lo, plan.node_hi, plan.edge_lo, plan.edge_hi
     n_edges_total, n_edges_local = graph.src.numel(), e1 - e0
@@ -276,13 +458,13 @@ def main():
     egraph = EdgeGraph(plan.src_local.to(dev), plan.dst_local.to(dev), plan.num_local, plan.num_owned)
     send_index = plan.send_index.to(dev)
     layer = enn.SO3LinearGraph(IRREPS, IRREPS, IRREPS, CHANNELS, CHANNELS, internal_weights=False,
-                               feature_mode="uv").to(dev)
+                               feature_mode=mode).to(dev)
     w_dev = weight.to(dev).requires_grad_(True)
     sh = enn.SphericalHarmonics(L_MAX)
     x_dev = x_host.to(dev).requires_grad_(True)
     vec_dev = vec_host.to(dev).requires_grad_(True)
     loss_host = torch.empty(2, dtype=torch.float32).pin_memory()             # two slots: results are read one step late
-    gw_host = torch.empty(2, PATHS, CHANNELS, CHANNELS).pin_memory()
+    gw_host = torch.empty(2, *weight.shape).pin_memory()
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev) if args.workload == "cfg2" else None
 
     def step(x, vec):
@@ -356,20 +538,38 @@ def main():
             dist.all_reduce(flag, op=dist.ReduceOp.MIN)
             if int(flag.item()) == 0:
                 graphed = None
+    repeat_ms = [elapsed_ms]
     if graphed is not None:
         for _ in range(3):
             graphed[0].replay()
         check_status()
-        barrier()
-        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0.record()
-        for i in range(args.steps):
-            graphed[i % 2].replay()
-        t1.record()
-        barrier()
-        elapsed_ms = t0.elapsed_time(t1)
+        repeat_ms = []
+        for _ in range(max(1, args.repeats)):       # the timed region of K steps, repeated; the median is reported
+            barrier()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for i in range(args.steps):
+                graphed[i % 2].replay()
+            t1.record()
+            barrier()
+            repeat_ms.append(t0.elapsed_time(t1))
         check_status()
     clocks = sampler.stop()
+    rep = torch.tensor(repeat_ms, dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(rep, op=dist.ReduceOp.MAX)          # every repeat: the slowest rank
+    repeat_ms = sorted(float(v) for v in rep.tolist())
+    elapsed_ms = repeat_ms[len(repeat_ms) // 2] if len(repeat_ms) % 2 else 0.5 * (repeat_ms[len(repeat_ms) // 2 - 1] + repeat_ms[len(repeat_ms) // 2])
+
+    # ---- checksum of one step (comparable across N: everything is summed over ranks) ----------------
+    out_c, gx_c, gv_c, gw_c = step(x_dev, vec_dev)
+    sums = torch.stack([torch.dot(out_c.double().reshape(-1), cot.double().reshape(-1)), gx_c.double().sum(),
+                        gx_c.double().square().sum(), gv_c.double().sum(), gv_c.double().square().sum()])
+    if world > 1:
+        dist.all_reduce(sums)
+    checksum = {"loss": float(sums[0]), "gw_norm": float(gw_c.double().norm()), "gx_sum": float(sums[1]),
+                "gx_norm": float(sums[2]) ** 0.5, "gv_sum": float(sums[3]), "gv_norm": float(sums[4]) ** 0.5}
+    del out_c, gx_c, gv_c, gw_c
 
     # ---- end-to-end timing: host buffers in, result out, every step ----------------------------
     # Every step copies its own inputs from pinned host memory and reads its result back.  The copy of step
@@ -424,10 +624,10 @@ def main():
     e2e_ms = e0_.elapsed_time(e1_)
     check_status()
 
-    times = torch.tensor([elapsed_ms, e2e_ms, eager_ms], dtype=torch.float64, device=dev)
+    times = torch.tensor([e2e_ms, eager_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    elapsed_ms, e2e_ms, eager_ms = (float(v) for v in times.tolist())
+    e2e_ms, eager_ms = (float(v) for v in times.tolist())
     steps = max(1, args.steps)
     value = n_edges_total * steps / (elapsed_ms * 1e-3)
     e2e_value = n_edges_total * steps / (e2e_ms * 1e-3)
@@ -440,10 +640,10 @@ def main():
         "cg_segment_sum[fwd]": n_edges_local * (row_bytes + DIM * 4 + 8) + n_dst * (s_bytes + 8),
         "cg_segment_sum[grad_x]": n_edges_local * (row_bytes + DIM * 4 + 16) + n_src * (s_bytes + 8),
         "cg_inner[grad_y]": n_edges_local * (row_bytes + DIM * 4 + 8) + n_dst * (s_bytes + 8),
-        "channel_mix[fwd]": n_dst * (s_bytes + row_bytes) + PATHS * CHANNELS * CHANNELS * 4,
-        "channel_mix[grad_inter]": n_dst * (s_bytes + row_bytes) + PATHS * CHANNELS * CHANNELS * 4,
-        "channel_mix[grad_x]": n_src * (s_bytes + row_bytes) + PATHS * CHANNELS * CHANNELS * 4,
-        "weight_grad": n_dst * (s_bytes + row_bytes) + PATHS * CHANNELS * CHANNELS * 4,
+        "channel_mix[fwd]": n_dst * (s_bytes + row_bytes) + weight.numel() * 4,
+        "channel_mix[grad_inter]": n_dst * (s_bytes + row_bytes) + weight.numel() * 4,
+        "channel_mix[grad_x]": n_src * (s_bytes + row_bytes) + weight.numel() * 4,
+        "weight_grad": n_dst * (s_bytes + row_bytes) + weight.numel() * 4,
         "spherical_harmonics[fwd]": n_edges_local * (12 + DIM * 4),
         "spherical_harmonics[bwd]": n_edges_local * (12 + DIM * 4 + 12),
     }
@@ -471,21 +671,33 @@ def main():
                     "unit": "GB/s", "frac": table[top]["frac_of_hbm_peak"], "peak_source": pk["source"],
                     "algorithmic_bytes_per_launch": algorithmic.get(top),
                     "traffic": (int(ncu_dram_bytes_cfg5q[top] * n_edges_local / 499040)
-                                if top in ncu_dram_bytes_cfg5q else None)}
+                                if top in ncu_dram_bytes_cfg5q else None),
+                    "traffic_source": ("ncu capture of the 499,040-edge profiling workload (profiles/), scaled by edges; "
+                                       "a lower bound for the gathering kernels (its node table fits L2)"
+                                       if top in ncu_dram_bytes_cfg5q else None),
+                    # whole step against the operator-boundary traffic of the per-edge layer (20,672 B per edge: x, y,
+                    # out forward; g, x, y, gx, gy backward) - the figure the 70 % target is stated on
+                    "step_frac_opboundary": round(20672.0 * value / 1e9 / pk["hbm_gbs"], 4),
+                    "step_opboundary_bytes_per_edge": 20672}
 
     result = {
         "metric": METRIC, "value": value, "unit": "edges/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": elapsed_ms / steps, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "repeats": {"count": len(repeat_ms), "ms_per_step_min": repeat_ms[0] / steps, "ms_per_step_max": repeat_ms[-1] / steps,
+                    "value_is": "median over the repeats of K steps (each the maximum over ranks)"},
+        "checksum": checksum,
         "config": {"workload": label, "edges": n_edges_total, "nodes": graph.num_nodes, "irreps": IRREPS,
-                   "channels": CHANNELS, "feature_mode": "uv", "paths": PATHS,
+                   "channels": CHANNELS, "feature_mode": mode, "paths": PATHS,
                    "parallelism": f"edges sharded by destination-node range over {world} GPU(s), halo rows by all-to-all",
                    "l2": ("working set >> 126 MB L2, no flush" if flush is None
                           else "256 MB written between steps to flush L2; steps timed individually")},
         "e2e": {"value": e2e_value, "unit": "edges/s", "ms_per_step": e2e_ms / steps,
                 "h2d_bytes_per_step": int(x_host.numel() * 4 + vec_host.numel() * 4) * world if world == 1
                 else int(x_all.numel() * 4 + graph.edge_vec.numel() * 4),
-                "d2h_bytes_per_step": int(4 + gw_host[0].numel() * 4) * world},
+                "d2h_bytes_per_step": int(4 + gw_host[0].numel() * 4) * world,
+                "copied_back": "loss <out, cotangent> and the weight gradient; out, grad_x and grad_vec stay on the device "
+                               "as they would in a training step"},
         "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "kernels": table,
         "host_enqueue_ms_per_step": (round(host_enqueue_ms / steps, 3) if host_enqueue_ms is not None else None),
         "cuda_graph": graphed is not None, "cuda_graph_error": graph_error,
@@ -493,7 +705,7 @@ def main():
     }
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
-            result["cpu_baseline"] = cpu_baseline(graph, x_all, cot_all, weight)
+            result["cpu_baseline"] = cpu_baseline(graph, x_all, cot_all, weight, mode)
         print(json.dumps(result), flush=True)
     # Tear down in a fixed order: graphs that captured collectives first, then the process group.  Destroying the
     # NCCL communicator while such graphs were alive left the ranks waiting at exit; after the final barrier every

@@ -1,8 +1,10 @@
 """Import the reference implementation from a read-only checkout.
 
-Only used by the fixture generator (``make_golden.py``) and by optional
-cross-checks that are skipped when the checkout is absent; nothing that runs on
-a GPU machine imports this module.
+Used by the fixture generators (``make_golden*.py``), by optional cross-checks that are
+skipped when the checkout is absent, and by the CPU arm of ``bench.py``, which points
+``EQUITORCH_REFERENCE_ROOT`` at the unmodified install of the reference under
+``baseline/_ref`` to time the reference's own CPU code.  No test that runs on a GPU
+machine needs the checkout.
 
 The reference imports ``torch_geometric`` for two CPU reductions (``segment``,
 ``scatter``) and a few names it never calls on this path.  That package is not
