@@ -2,7 +2,7 @@
 (l_max = 3, 64 channels, full 64 -> 64 channel mixing per path), on N GPUs of one box.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg5|cfg5q|cfg2|cfg1|cfg3|cfg4|epilogue]
-                    [--feature-mode uv|uu] [--repeats R] [--impl ours|reference] [--no-graph] [--no-cpu-baseline]
+                    [--feature-mode uv|uu] [--repeats R] [--impl ours|reference|reference_triton] [--no-graph] [--no-cpu-baseline]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
 One step = one pass of the layer over one synthetic graph: spherical harmonics of the edge vectors,
@@ -218,6 +218,56 @@ def cpu_baseline(graph, x, cot, weight, mode="uv", max_edges=32768, repeats=2, c
             "port": port}
 
 
+def run_reference_triton(args):
+    """The reference's own GPU path (its Triton kernels, unmodified, from baseline/_ref) on this GPU: per-edge
+    SO3Linear at l_max 3, 64 channels, E = 20,000 (its per-edge intermediate is 25 KB per edge), 'uu' and 'uv',
+    forward + backward.  A second, same-box bar beside the CPU arm; prints one JSON line, `unavailable` with
+    the error message if the kernels do not compile or launch here."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    line = {"impl": "reference_triton", "metric": METRIC, "unit": "edges/s", "n_gpus": 1, "dtype": "f32", "data": "synthetic"}
+    try:
+        if not reference_available():
+            raise RuntimeError("baseline/_ref is absent")
+        os.environ["EQUITORCH_REFERENCE_ROOT"] = REF_DIR
+        from tests.golden._reference_import import import_reference
+        import_reference()
+        from equitorch.nn.linears import SO3Linear as RefSO3Linear
+        from equitorch.nn.sphericals import SphericalHarmonics as RefSH
+        dev = torch.device("cuda", 0)
+        e = 20_000
+        gen = torch.Generator().manual_seed(0)
+        x = torch.randn(e, DIM, CHANNELS, generator=gen).to(dev).requires_grad_(True)
+        v = torch.randn(e, 3, generator=gen).to(dev).requires_grad_(True)
+        cot = torch.randn(e, DIM, CHANNELS, generator=gen).to(dev)
+        res = {}
+        for mode in ("uu", "uv"):
+            layer = RefSO3Linear(IRREPS, IRREPS, IRREPS, CHANNELS, CHANNELS, internal_weights=False, feature_mode=mode).to(dev)
+            shape = (PATHS, CHANNELS) if mode == "uu" else (PATHS, CHANNELS, CHANNELS)
+            w = ((torch.rand(*shape, generator=gen) * 2 - 1) * 0.2).to(dev).requires_grad_(True)
+            sh = RefSH(L_MAX)
+
+            def step():
+                out = layer(x, sh(v), w)
+                return torch.autograd.grad(out, [x, v, w], cot)
+            for _ in range(max(3, args.warmup)):
+                step()
+            torch.cuda.synchronize(dev)
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(args.steps):
+                step()
+            t1.record()
+            torch.cuda.synchronize(dev)
+            ms = t0.elapsed_time(t1) / max(1, args.steps)
+            res[mode] = {"edges_per_s": e / (ms * 1e-3), "ms_per_step": ms}
+        line.update({"value": res["uv"]["edges_per_s"], "edges": e, "modes": res, "steps": args.steps,
+                     "config": {"workload": "per-edge SO3Linear (no gather, no reduction), 20,000 edges, l_max 3, 64 channels"}})
+    except Exception as exc:  # noqa: BLE001 - any failure of the reference's GPU path is the result
+        line["unavailable"] = f"{type(exc).__name__}: {exc}"[:400]
+    print(json.dumps(line), flush=True)
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -414,12 +464,14 @@ def main():
     ap.add_argument("--feature-mode", default="uv", choices=["uv", "uu"],
                     help="uv: 64 x 64 channel mixing per path (the metric); uu: channel-wise weights per path")
     ap.add_argument("--repeats", type=int, default=5, help="how often the timed region of K steps is repeated (median reported)")
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference_triton"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time the eager step only (no CUDA-graph replay)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.impl == "reference_triton":
+        return run_reference_triton(args)
     if args.workload == "epilogue":
         return run_epilogue(args)
     if args.workload in ("cfg1", "cfg3", "cfg4"):

@@ -27,7 +27,12 @@ def test_oracle_matches_reference_fixture(key):
 @pytest.mark.parametrize("key", sorted(GOLD["cases"]))
 def test_module_matches_reference_fixture(key, dtype, tol):
     case = GOLD["cases"][key]
-    mod = enn.TensorDot(key.split("/")[0], "uu", scaled=case["scaled"]).to(DEV)
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(dtype)          # the 1 / sqrt(2l + 1) table is built in the default dtype, as in the reference
+    try:
+        mod = enn.TensorDot(key.split("/")[0], "uu", scaled=case["scaled"]).to(DEV)
+    finally:
+        torch.set_default_dtype(prev)
     a, b = (case[k].to(DEV, dtype).requires_grad_(True) for k in ("a", "b"))
     out = mod(a, b)
     ga, gb = torch.autograd.grad(out, [a, b], case["cot"].to(DEV, dtype))
