@@ -132,16 +132,6 @@ def outer_order(s: Structure) -> np.ndarray:
     return out
 
 
-def cell_table(s: Structure):
-    """Entries grouped by cell (m_y, m_feat) for the adjoint kernel, which keeps one cell per lane:
-    ``cell_ptr`` (d_y * d_feat + 1), ``cell_row`` (T), ``cell_entry`` (T; the entry id, for its scale), and the largest
-    number of entries in one cell."""
-    cell = s.my * s.d_feat + s.mf
-    order = np.argsort(cell, kind="stable")
-    ptr = np.searchsorted(cell[order], np.arange(s.d_y * s.d_feat + 1)).astype(np.int64)
-    return ptr, s.row[order].astype(np.int64), order.astype(np.int64), int(np.diff(ptr).max()) if len(cell) else 0
-
-
 def _emit_outer_role(s: Structure, plan: OuterPlan, w: int) -> List[str]:
     """Functions of warp role ``w``.  A lane holds CPL channels; ``xr`` points at its channels of the
     staged feature row (component stride C floats), loaded component by component just before use."""
