@@ -48,6 +48,11 @@ class TpTableStruct(C.Structure):
                 ("structure_key", C.c_uint64), ("scale_o", C.c_void_p)]
 
 
+class WignerTableStruct(C.Structure):
+    _fields_ = [("coef", C.c_void_p), ("comp", C.c_void_p), ("blocks", C.c_void_p), ("dim", C.c_int32),
+                ("num_blocks", C.c_int32), ("max_l", C.c_int32), ("coef_count", C.c_int32)]
+
+
 class MixBlockStruct(C.Structure):
     _fields_ = [("in_row0", C.c_int32), ("out_row0", C.c_int32), ("dim", C.c_int32), ("paths", C.c_int32),
                 ("w_offset", C.c_int64)]
@@ -77,6 +82,14 @@ SIGNATURES = {
                                       C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]),
     "eqt_wgrad_tc_static_capacity": (C.c_int64, []),
     "eqt_wgrad_tc_scratch_floats": (C.c_int64, [C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_int32]),
+    "eqt_wigner_d_forward": (C.c_int, [C.POINTER(WignerTableStruct), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                       C.c_int32, C.c_void_p]),
+    "eqt_wigner_d_backward": (C.c_int, [C.POINTER(WignerTableStruct), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                        C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p]),
+    "eqt_dense_rotation": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                     C.c_void_p]),
+    "eqt_dense_rotation_grad_matrix": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32,
+                                                 C.c_void_p]),
     "eqt_pack_weights": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_int32,
                                    C.c_void_p, C.c_void_p, C.c_void_p]),
     "eqt_irrep_scale": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,

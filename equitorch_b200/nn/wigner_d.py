@@ -6,7 +6,7 @@ from torch import Tensor, nn
 
 from ..irreps import Irreps, check_irreps
 from ..tables import wigner_d_info
-from .functional.wigner_d import sparse_wigner_rotation, wigner_d_matrix
+from .functional.wigner_d import dense_wigner_rotation, sparse_wigner_rotation, wigner_d_matrix
 
 
 class _WithRotationInfo(nn.Module):
@@ -42,7 +42,7 @@ class DenseWignerRotation(nn.Module):
         self.irreps = check_irreps(irreps)
 
     def forward(self, input: Tensor, wigner_d: Tensor) -> Tensor:
-        return wigner_d @ input
+        return dense_wigner_rotation(input, wigner_d)
 
     def extra_repr(self) -> str:
         return f"irreps={self.irreps}"
@@ -61,7 +61,8 @@ class WignerD(_WithRotationInfo):
     def forward(self, alpha: Optional[Tensor] = None, beta: Optional[Tensor] = None, gamma: Optional[Tensor] = None,
                 sincos_alpha: Optional[Tensor] = None, sincos_beta: Optional[Tensor] = None,
                 sincos_gamma: Optional[Tensor] = None) -> Tensor:
-        return wigner_d_matrix(self.identity, alpha, beta, gamma, sincos_alpha, sincos_beta, sincos_gamma, self.info)
+        return wigner_d_matrix(self.identity, alpha, beta, gamma, sincos_alpha, sincos_beta, sincos_gamma, self.info,
+                               irreps=self.irreps)
 
     def extra_repr(self) -> str:
         return f"irreps={self.irreps}"

@@ -135,7 +135,7 @@ def cfg4(dev, edges: int = 100_000) -> Workload:
 
     def step():
         d = wig(ad[:, 0], ad[:, 1], ad[:, 2])
-        out = d.transpose(-1, -2) @ layer(dense(xd, d), w)
+        out = dense(layer(dense(xd, d), w), d.transpose(-1, -2))
         gx, ga, gw = torch.autograd.grad(out, [xd, ad, w], cot)
         return torch.dot(out.reshape(-1), cot.reshape(-1)).reshape(1), [gw, gx, ga]
 

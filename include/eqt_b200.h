@@ -313,6 +313,40 @@ int eqt_layer_rms_backward(const void* x, const void* grad_out, const void* weig
                            void* grad_weight_partial, const int64_t* irrep_seg, int64_t n, int32_t d, int32_t k,
                            int32_t c, int32_t scaled, int32_t dtype, void* stream);
 
+/*
+ * Wigner-D matrices of ZYZ Euler angles,  D = Z(alpha) J Z(beta) J Z(gamma)  per irrep block (real basis, component
+ * order m = -l..l, Z(a): x'_m = cos(m a) x_m - sign(m) sin(|m| a) x_{-m}), written as a dense block-diagonal
+ * (n, dim, dim) tensor in one pass, and the gradient of a scalar with respect to the three angles from grad_d
+ * (only the in-block elements of grad_d are read).  The table holds, per irrep block of degree l, the coefficients
+ * of the trigonometric polynomial  J Z(beta) J = sum_k A_k cos(k beta) + B_k sin(k beta):  (l + 1) x (2l+1) x (2l+1) x 2
+ * values [k][a][b][A, B] in the dtype of the call.  float32 / float64, degrees up to 7.
+ * replaces: wigner_d_matrix (equitorch/nn/functional/wigner_d.py:74-139: sincos :4-35 of nn/functional/angular.py,
+ *   three sparse_vecsca z-rotations and two sparse_scale J passes over the identity) and its autograd chain.
+ */
+typedef struct eqt_wigner_table {
+  const void* coef;        /* device, coef_count values                                                  */
+  const int32_t* comp;     /* device (dim, 4): first component of the block, l, coefficient offset, m    */
+  const int32_t* blocks;   /* device (num_blocks, 3): first component, l, coefficient offset             */
+  int32_t dim, num_blocks, max_l, coef_count;
+} eqt_wigner_table;
+int eqt_wigner_d_forward(const eqt_wigner_table* table, const void* alpha, const void* beta, const void* gamma, void* d,
+                         int64_t n, int32_t dtype, void* stream);
+int eqt_wigner_d_backward(const eqt_wigner_table* table, const void* alpha, const void* beta, const void* gamma,
+                          const void* grad_d, void* grad_alpha, void* grad_beta, void* grad_gamma, int64_t n,
+                          int32_t dtype, void* stream);
+
+/*
+ * Dense rotation of features by a per-sample matrix:  out[n, i, c] = sum_j matrix[n, i, j] x[n, j, c]  (with
+ * `transposed`: matrix[n, j, i]), matrix (n, dim, dim), x / out (n, dim, channels), and the gradient with respect
+ * to the matrix, grad_matrix[n, i, j] = sum_c grad_out[n, i, c] x[n, j, c].  float32 / float64.
+ * replaces: dense_wigner_rotation = `wigner_d @ input` (equitorch/nn/functional/wigner_d.py:58-72,
+ *   equitorch/nn/wigner_d.py:89-106) and the two batched products of its backward pass.
+ */
+int eqt_dense_rotation(const void* matrix, const void* x, void* out, int64_t n, int32_t dim, int32_t channels,
+                       int32_t transposed, int32_t dtype, void* stream);
+int eqt_dense_rotation_grad_matrix(const void* grad_out, const void* x, void* grad_matrix, int64_t n, int32_t dim,
+                                   int32_t channels, int32_t dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
