@@ -65,6 +65,7 @@ struct MixLaunch {
 
 #include "mix_tc_kernel.inc"
 #include "wgrad_tc_kernel.inc"
+#include "vecmat_tc_kernel.inc"
 
 // ------------------------------------------------------------------------------------------
 // host side
@@ -307,6 +308,133 @@ extern "C" int eqt_wgrad_tc(const float* s, const float* g, float* gw_packed, fl
     if (int rc = check_launch("wgrad_reduce_kernel")) return rc;
   }
   return EQT_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// The reference's indexed products with shared weights on the same machinery
+// ------------------------------------------------------------------------------------------
+extern "C" int eqt_vecmat_tc(const float* x, const float* w, const int64_t* index2, const float* scale, float* w_big,
+                             float* w_small, float* out, int64_t n, int32_t rows1, int32_t cin, int32_t cout,
+                             int32_t num_out, int64_t entries, const int32_t* kb_begin, const int32_t* a_col,
+                             int32_t* status, void* stream) {
+  using namespace eqt;
+  if (n < 0 || rows1 <= 0 || cin <= 0 || cout <= 0 || num_out < 0 || entries < 0) return fail(EQT_ERR_BAD_ARGUMENT, "bad sizes");
+  if (n == 0 || num_out == 0) return EQT_OK;
+  if (!x || !w || !w_big || !w_small || !out || !kb_begin || !a_col || !status) return fail(EQT_ERR_BAD_ARGUMENT, "NULL pointer");
+  if (cin % KB != 0 || cout % 16 != 0 || cout > 128)
+    return fail(EQT_ERR_UNSUPPORTED, "tensor-core vecmat needs C_in %% 32 == 0, C_out %% 16 == 0, C_out <= 128");
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(w_big) |
+       reinterpret_cast<uintptr_t>(w_small)) & 15u)
+    return fail(EQT_ERR_UNSUPPORTED, "tensor-core vecmat needs 16-byte aligned operands");
+  if (n > 0x7fffffffll || (int64_t)rows1 * cin > 0x7fffffffll || entries * cin > 0x7fffffffll)
+    return fail(EQT_ERR_UNSUPPORTED, "operands too large for one TMA coordinate");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t ktot = entries * cin;
+  if (entries > 0) {
+    pack_vecmat_weights_kernel<<<flat_grid(ktot * cout, 256), 256, 0, st>>>(w, index2, scale, w_big, w_small, entries, cin, cout);
+    if (int rc = check_launch("pack_vecmat_weights_kernel")) return rc;
+  }
+  VecmatLaunch L{};
+  L.out = out; L.kb_begin = kb_begin; L.a_col = a_col; L.n = n; L.num_out = num_out; L.n_cols = cout; L.status = status;
+  L.total_items = (int64_t)num_out * ceil_div(n, TILE_M);
+  const uint32_t stage_bytes = TILE_M * KB * 4 + 2u * (uint32_t)cout * KB * 4;
+  L.stages = (int)std::min<size_t>(std::min<size_t>(8, (220 * 1024 - 1024) / stage_bytes), (512 - 2 * cout) / 64);
+  if (L.stages < 2) return fail(EQT_ERR_UNSUPPORTED, "tile too wide for the shared-memory ring");
+  L.tmem_cols = 32;
+  while (L.tmem_cols < 2 * cout + 64 * L.stages) L.tmem_cols <<= 1;
+  {
+    cuuint64_t dims[3] = {(cuuint64_t)rows1 * cin, 1, (cuuint64_t)n};
+    cuuint64_t strides[2] = {(cuuint64_t)rows1 * cin * 4, (cuuint64_t)rows1 * cin * 4};
+    cuuint32_t box[3] = {KB, 1, TILE_M};
+    if (int rc = make_map(&L.map_a, x, 3, dims, strides, box)) return rc;
+  }
+  {
+    // an empty table still needs valid maps: describe at least one k-block
+    cuuint64_t dims[2] = {(cuuint64_t)std::max<int64_t>(ktot, KB), (cuuint64_t)cout};
+    cuuint64_t strides[1] = {(cuuint64_t)std::max<int64_t>(ktot, KB) * 4};
+    cuuint32_t box[2] = {KB, (cuuint32_t)cout};
+    if (int rc = make_map(&L.map_bb, w_big, 2, dims, strides, box)) return rc;
+    if (int rc = make_map(&L.map_bs, w_small, 2, dims, strides, box)) return rc;
+  }
+  cudaError_t e = cudaFuncSetAttribute(vecmat_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+  if (e != cudaSuccess) return fail(EQT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  const unsigned grid = (unsigned)std::min<int64_t>(L.total_items, sm_count());
+  vecmat_tc_kernel<<<grid, TC_THREADS, (size_t)L.stages * stage_bytes + 1024, st>>>(L);
+  return check_launch("vecmat_tc_kernel");
+}
+
+extern "C" int64_t eqt_outer_tc_scratch_floats(int64_t n, int32_t c2, int32_t m_tiles) {
+  using namespace eqt;
+  if (n < 0 || c2 <= 0 || c2 % 32 || m_tiles <= 0) return -1;
+  const int splits = std::max(1, sm_count() / m_tiles);
+  return (int64_t)splits * m_tiles * 128 * c2;
+}
+
+extern "C" int eqt_outer_tc(const float* in1, const float* in2, float* out, float* scratch, int64_t scratch_floats, int64_t n,
+                            int32_t rows1, int32_t c1, int32_t rows2, int32_t c2, const int32_t* a_cols, const int32_t* b_cols,
+                            int32_t m_tiles, const int32_t* red_ptr, const int32_t* red_slot, const float* red_scale,
+                            int32_t num_w, int32_t* status, void* stream) {
+  using namespace eqt;
+  if (n < 0 || rows1 <= 0 || rows2 <= 0 || c1 <= 0 || c2 <= 0 || m_tiles < 0 || num_w < 0) return fail(EQT_ERR_BAD_ARGUMENT, "bad sizes");
+  if (num_w == 0) return EQT_OK;
+  if (!in1 || !in2 || !out || !scratch || !a_cols || !b_cols || !red_ptr || !red_slot || !red_scale || !status)
+    return fail(EQT_ERR_BAD_ARGUMENT, "NULL pointer");
+  if (c1 % 32 != 0 || c2 % 32 != 0 || c2 > 128)
+    return fail(EQT_ERR_UNSUPPORTED, "tensor-core outer product needs C1 %% 32 == 0, C2 %% 32 == 0, C2 <= 128");
+  if ((reinterpret_cast<uintptr_t>(in1) | reinterpret_cast<uintptr_t>(in2) | reinterpret_cast<uintptr_t>(out) |
+       reinterpret_cast<uintptr_t>(scratch)) & 15u)
+    return fail(EQT_ERR_UNSUPPORTED, "tensor-core outer product needs 16-byte aligned operands");
+  if (n > 0x7fffffffll || (int64_t)rows1 * c1 > 0x7fffffffll || (int64_t)rows2 * c2 > 0x7fffffffll)
+    return fail(EQT_ERR_UNSUPPORTED, "operands too large for one TMA coordinate");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int splits = 1;
+  if (n > 0 && m_tiles > 0) {
+    const int b_boxes = c2 / 32;
+    const size_t budget = 220 * 1024 - 1024;
+    const size_t bytes_per_row = 2 * (size_t)(4 + b_boxes) * 128;
+    const int npt = (int)std::min<size_t>(128, budget / 2 / bytes_per_row) / 8 * 8;      // reduction rows per tile
+    WgradArgs a{};
+    a.n = n; a.dim = 1; a.npt = npt; a.n_cols = c2; a.status = status;
+    const size_t stage_bytes = bytes_per_row * (size_t)npt;
+    a.stages = (int)std::min<size_t>(4, budget / stage_bytes);
+    a.tmem_cols = 32;
+    while (a.tmem_cols < 2 * c2) a.tmem_cols <<= 1;
+    a.chunk_tiles = std::max(1, 512 / npt);
+    a.a_cols = a_cols; a.b_cols = b_cols;
+    const int64_t tiles = ceil_div(n, npt);
+    splits = (int)std::max<int64_t>(1, std::min<int64_t>(tiles, sm_count() / m_tiles));
+    const int64_t need = (int64_t)splits * m_tiles * 128 * c2;
+    if (need > scratch_floats) return fail(EQT_ERR_BAD_ARGUMENT, "scratch too small: %lld floats needed", (long long)need);
+    a.partial = scratch;
+    CUtensorMap map_a, map_b;
+    {
+      cuuint64_t dims[3] = {(cuuint64_t)rows1 * c1, 1, (cuuint64_t)n};
+      cuuint64_t strides[2] = {(cuuint64_t)rows1 * c1 * 4, (cuuint64_t)rows1 * c1 * 4};
+      cuuint32_t box[3] = {KB, 1, (cuuint32_t)npt};
+      if (int rc = make_map(&map_a, in1, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return rc;
+    }
+    {
+      cuuint64_t dims[3] = {(cuuint64_t)rows2 * c2, 1, (cuuint64_t)n};
+      cuuint64_t strides[2] = {(cuuint64_t)rows2 * c2 * 4, (cuuint64_t)rows2 * c2 * 4};
+      cuuint32_t box[3] = {KB, 1, (cuuint32_t)npt};
+      if (int rc = make_map(&map_b, in2, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return rc;
+    }
+    cudaError_t e = cudaFuncSetAttribute(wgrad_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    if (e != cudaSuccess) return fail(EQT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    dim3 grid((unsigned)splits, (unsigned)m_tiles);
+    wgrad_tc_kernel<<<grid, TC_THREADS, (size_t)a.stages * stage_bytes + 1024, st>>>(map_a, map_b, a);
+    if (int rc = check_launch("wgrad_tc_kernel")) return rc;
+  }
+  // with no samples or no entries every unit list is read as empty only if m_tiles == 0; otherwise the partial sums
+  // above were written by this call
+  if (n == 0 || m_tiles == 0) {
+    cudaError_t e = cudaMemsetAsync(out, 0, sizeof(float) * (size_t)num_w * c1 * c2, st);
+    if (e != cudaSuccess) return fail(EQT_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+    return EQT_OK;
+  }
+  outer_reduce_kernel<<<flat_grid((int64_t)num_w * c1 * c2 / 4, 256), 256, 0, st>>>(scratch, out, red_ptr, red_slot, red_scale, splits,
+                                                                                   (int64_t)m_tiles * 128, num_w, c1, c2);
+  return check_launch("outer_reduce_kernel");
 }
 
 // ------------------------------------------------------------------------------------------

@@ -233,11 +233,21 @@ __global__ void __launch_bounds__(128) dense_rotation_kernel(const T* __restrict
 #pragma unroll
           for (int w = 0; w < 4; ++w) acc[u][w] += mv.v[u] * xv.v[w];
       }
+      const bool vec = (c & 3) == 0 && (reinterpret_cast<uintptr_t>(o) & 15u) == 0;
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
+      for (int u = 0; u < 4; ++u) {
+        if (r0 + u >= dim) break;
+        if (vec) {
+          Vec4<T> v;
 #pragma unroll
-        for (int w = 0; w < 4; ++w)
-          if (r0 + u < dim && ch + w < c) o[(r0 + u) * c + ch + w] = acc[u][w];
+          for (int w = 0; w < 4; ++w) v.v[w] = acc[u][w];
+          *reinterpret_cast<Vec4<T>*>(o + (r0 + u) * c + ch) = v;
+        } else {
+#pragma unroll
+          for (int w = 0; w < 4; ++w)
+            if (ch + w < c) o[(r0 + u) * c + ch + w] = acc[u][w];
+        }
+      }
     }
   }
 }
@@ -357,9 +367,9 @@ extern "C" int eqt_dense_rotation(const void* matrix, const void* x, void* out, 
   if (n == 0) return EQT_OK;
   if (!matrix || !x || !out) return fail(EQT_ERR_BAD_ARGUMENT, "NULL pointer");
   const size_t es = dtype == EQT_F32 ? 4 : 8;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
   const size_t bytes = es * ((size_t)dim * ((dim + 3) & ~3) + (size_t)dim * ((channels + 3) & ~3));
   if (bytes > 200 * 1024) return fail(EQT_ERR_UNSUPPORTED, "matrix and features of one sample do not fit shared memory");
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned grid = flat_grid(n, 1, 16);
   if (dtype == EQT_F32) {
     cudaFuncSetAttribute(dense_rotation_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);

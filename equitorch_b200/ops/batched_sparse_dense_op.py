@@ -30,6 +30,7 @@ import torch
 from torch import Tensor
 
 from .. import _lib
+from . import indexed_tc_op as _tc
 
 _ARITH = {torch.float32: torch.float32, torch.bfloat16: torch.float32, torch.float64: torch.float64}
 
@@ -90,7 +91,7 @@ def sparse_product(op: int, input1: Tensor, input2: Optional[Tensor], scale=None
             y, shared2, n2 = y[0], True, None
         else:
             raise ValueError(f"batch sizes differ: {n1} vs {n2}")
-    n = max(n1 or 1, n2 or 1)
+    n = max((v for v in (n1, n2) if v is not None), default=1)
 
     index1 = _index(index1, "index1", dev)
     index2 = _index(index2, "index2", dev)
@@ -110,6 +111,14 @@ def sparse_product(op: int, input1: Tensor, input2: Optional[Tensor], scale=None
         num_out = rows1
     if out_size is None:
         out_size = num_out
+
+    # GEMM-shaped cases with an operand shared by the batch go to the tensor cores (float32, channels % 32 == 0)
+    if out is None and op == _lib.OP_VECMAT and not shared1 and shared2 \
+            and _tc.vecmat_supported(x, y, gather_index, index_out, out_accumulated, out_size, num_out):
+        return _tc.vecmat_tc(x, y, scale, index1, index2, seg, num_out)
+    elif out is None and op == _lib.OP_OUTER and not shared1 and not shared2 \
+            and _tc.outer_supported(x, y, gather_index, index_out, out_accumulated, out_size, num_out):
+        return _tc.outer_tc(x, y, scale, index1, index2, seg, num_out)
 
     tail = {_lib.OP_OUTER: (c1, c2), _lib.OP_INNER: (), _lib.OP_VECMAT: (c2,)}.get(op, (c1,))
     lead = (out_size,) if out_accumulated else (n, out_size)

@@ -238,6 +238,46 @@ int eqt_wgrad_tc(const float* s, const float* g, float* gw_packed, float* scratc
 int64_t eqt_wgrad_tc_scratch_floats(int64_t n, int32_t cin, int32_t cout, const eqt_mix_block* blocks, int32_t num_blocks);
 
 /*
+ * The reference's indexed vector-matrix product with weights shared by the batch, on tensor cores (float32, 3xTF32):
+ *   out[i, M, co] = sum_{t in seg[M]} scale[t] * sum_ci x[i, index1[t], ci] * W[index2[t], ci, co]
+ * x (n, rows1, cin), W (.., cin, cout), out (n, num_out, cout).  Per output row M the entries of seg[M] form one
+ * GEMM over the samples whose k-blocks are 32-channel chunks of x rows; `kb_begin` (num_out + 1, device int32) is
+ * seg scaled to k-blocks (seg[M] * cin / 32) and `a_col` (entries * cin / 32, device int32) the column
+ * index1[t] * cin + 32 * chunk each k-block starts at - both depend on the table only and are built once.
+ * The weights are packed as Bt[co, t * cin + ci] = scale[t] * W[index2[t], ci, co] and split into TF32 big / small
+ * parts by this call into w_big / w_small (entries * cin * cout floats each, caller-owned scratch).  index2 / scale
+ * may be NULL (identity / ones).  Needs cin % 32 == 0, cout % 16 == 0, cout <= 128, 16-byte aligned pointers.
+ * `status` is set to 2 if a bounded wait expired.
+ * replaces: indexed_vecmat_scale_gather (equitorch/ops/batched_sparse_dense_op.py:1511-1534, kernel :1289-1381) for
+ *   a 3-D (shared) matrix operand, i.e. SO2Linear, IrrepWiseLinear, IrrepsLinear and the weight step of SO3Linear
+ *   'uv' (equitorch/nn/functional/linears.py:494-577, :263) and their input gradients.
+ */
+int eqt_vecmat_tc(const float* x, const float* w, const int64_t* index2, const float* scale, float* w_big,
+                  float* w_small, float* out, int64_t n, int32_t rows1, int32_t cin, int32_t cout, int32_t num_out,
+                  int64_t entries, const int32_t* kb_begin, const int32_t* a_col, int32_t* status, void* stream);
+
+/*
+ * The reference's indexed outer product accumulated over the batch (the gradient of shared weights), on tensor
+ * cores, deterministic:
+ *   out[w, a, b] = sum_i sum_{t in seg[w]} scale[t] * in1[i, index1[t], a] * in2[i, index2[t], b]
+ * in1 (n, rows1, c1), in2 (n, rows2, c2), out (num_w, c1, c2).  A "unit" is a 32-column chunk of an in1 row of
+ * one entry; units that share their in2 row are packed four to an M slice of 128 rows: a_cols (m_tiles * 4) holds
+ * the first in1 column of every slot (any valid column for padding slots), b_cols (m_tiles) the first in2 column of
+ * the slice.  Every CTA reduces a share of the samples for one slice on tcgen05 (TF32 big / small split, TMEM folded
+ * into float32 registers every ~512 samples); the per-CTA sums go through `scratch`
+ * (eqt_outer_tc_scratch_floats(n, c2, m_tiles) floats) and are combined in a fixed order:
+ * out[w, ci, :] = sum over the units u in [red_ptr[w * c1/32 + ci/32], red_ptr[.. + 1]) of red_scale[u] * (row
+ * red_slot[u] * 32 + ci % 32 of the summed slices).  No atomics.  Needs c1 % 32 == 0, c2 % 32 == 0, c2 <= 128.
+ * replaces: indexed_outer_scale_gather with out_accumulated=True (equitorch/ops/batched_sparse_dense_op.py:557-579,
+ *   kernel :343-434, which adds 32 x 32 tiles with tl.atomic_add).
+ */
+int eqt_outer_tc(const float* in1, const float* in2, float* out, float* scratch, int64_t scratch_floats, int64_t n,
+                 int32_t rows1, int32_t c1, int32_t rows2, int32_t c2, const int32_t* a_cols, const int32_t* b_cols,
+                 int32_t m_tiles, const int32_t* red_ptr, const int32_t* red_slot, const float* red_scale,
+                 int32_t num_w, int32_t* status, void* stream);
+int64_t eqt_outer_tc_scratch_floats(int64_t n, int32_t c2, int32_t m_tiles);
+
+/*
  * eqt_wgrad_tc for callers that cannot hand over a scratch buffer because they cannot allocate device
  * memory at the point of the call: a C or Fortran host program that links this library without a
  * CUDA allocator of its own, or a plug-in running inside a framework that reserved all device memory
