@@ -53,6 +53,18 @@ class WignerTableStruct(C.Structure):
                 ("num_blocks", C.c_int32), ("max_l", C.c_int32), ("coef_count", C.c_int32)]
 
 
+class RadiusGridStruct(C.Structure):
+    _fields_ = [("cell_start", C.c_void_p), ("sorted_index", C.c_void_p), ("point_cell", C.c_void_p), ("cell_size", C.c_float),
+                ("dims", C.c_int32 * 3)]
+
+
+class EdgeFeaturesStruct(C.Structure):
+    _fields_ = [("vec", C.c_void_p), ("length", C.c_void_p), ("sh", C.c_void_p), ("bessel", C.c_void_p), ("cutoff", C.c_void_p),
+                ("bessel_weights", C.c_void_p), ("l_max", C.c_int32), ("integral_normalize", C.c_int32), ("num_basis", C.c_int32),
+                ("cutoff_kind", C.c_int32), ("r_max", C.c_float), ("cutoff_r_min", C.c_float), ("cutoff_r_max", C.c_float),
+                ("cutoff_p", C.c_float), ("cutoff_eps", C.c_float)]
+
+
 class MixBlockStruct(C.Structure):
     _fields_ = [("in_row0", C.c_int32), ("out_row0", C.c_int32), ("dim", C.c_int32), ("paths", C.c_int32),
                 ("w_offset", C.c_int64)]
@@ -97,6 +109,10 @@ SIGNATURES = {
                                C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
                                C.c_int32, C.c_void_p, C.c_void_p]),
     "eqt_outer_tc_scratch_floats": (C.c_int64, [C.c_int64, C.c_int32, C.c_int32]),
+    "eqt_radius_count": (C.c_int, [C.POINTER(RadiusGridStruct), C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_int32, C.c_int32,
+                                   C.c_void_p, C.c_void_p, C.c_void_p]),
+    "eqt_radius_edges": (C.c_int, [C.POINTER(RadiusGridStruct), C.c_void_p, C.c_void_p, C.c_int64, C.c_float, C.c_int32, C.c_int32,
+                                   C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(EdgeFeaturesStruct), C.c_void_p, C.c_void_p]),
     "eqt_pack_weights": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_int32,
                                    C.c_void_p, C.c_void_p, C.c_void_p]),
     "eqt_irrep_scale": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,

@@ -1,6 +1,8 @@
 """Module API of the tensor-product path (same class names as ``equitorch.nn``)."""
 from . import functional  # noqa: F401
 from .activations import Gate
+from .cutoffs import CosineCutoff, MollifierCutoff, PolynomialCutoff
+from .radials import BesselBasis
 from .angular import SinCos
 from .graph_layers import SO3LinearGraph
 from .linears import IrrepsLinear, IrrepWiseLinear, SO2Linear, SO3Linear

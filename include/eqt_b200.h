@@ -387,6 +387,51 @@ int eqt_dense_rotation(const void* matrix, const void* x, void* out, int64_t n, 
 int eqt_dense_rotation_grad_matrix(const void* grad_out, const void* x, void* grad_matrix, int64_t n, int32_t dim,
                                    int32_t channels, int32_t dtype, void* stream);
 
+/*
+ * Radius graph and edge features in one pass over a cell list (float32).
+ * The caller bins the n points into cubic cells of side cell_size >= r - `dims` cells per axis, x fastest:
+ * cell = ((graph * dims[2] + z) * dims[1] + y) * dims[0] + x, one slab of cells per graph of the batch - and
+ * passes point_cell (n), the points' indices sorted by cell (sorted_index) and the first sorted position of every
+ * cell (cell_start, number of cells + 1), all int32 on the device.
+ * eqt_radius_count: degree[i] = min(#{j : |pos_i - pos_j| < r, same graph, j != i unless loop}, max_neighbors).
+ * eqt_radius_edges: with ptr = exclusive scan of degree (n + 1, int64), for every target i the max_neighbors
+ * neighbours of smallest index j, ascending, at e = ptr[i] + rank: src[e] = j, dst[e] = i and, where the pointer in
+ * `features` is not NULL,
+ *   vec[e]    = pos[i] - pos[j]                       length[e] = |vec[e]|
+ *   sh[e, :]  = real spherical harmonics of vec / max(|vec|, 1e-12), l <= l_max <= 4, component normalised
+ *               (times 1 / sqrt(4 pi) with integral_normalize)
+ *   bessel[e, b] = (2 / r_max) sin(bessel_weights[b] |vec| / r_max) / |vec|
+ *   cutoff[e] = polynomial (p) / cosine / mollifier (eps) envelope of u = clamp((|vec| - r_min) / (r_max - r_min), 0, 1)
+ * `status` is set to 1 if a target had more than 512 candidates (its list is then truncated).
+ * replaces: RadiusGraph, AddVectorNorm, AddSphericalHarmonics, AddVectorLengthEmbedding
+ *   (equitorch/transforms/__init__.py:18-251; the neighbour search itself is torch_geometric.nn.radius_graph, not
+ *   part of the reference's sources), BesselBasis (equitorch/nn/radials.py:10-56) and the cutoffs
+ *   (equitorch/nn/functional/cutoffs.py).
+ */
+enum eqt_cutoff_kind { EQT_CUTOFF_POLYNOMIAL = 0, EQT_CUTOFF_COSINE = 1, EQT_CUTOFF_MOLLIFIER = 2 };
+typedef struct eqt_radius_grid {
+  const int32_t* cell_start;
+  const int32_t* sorted_index;
+  const int32_t* point_cell;
+  float cell_size;
+  int32_t dims[3];
+} eqt_radius_grid;
+typedef struct eqt_edge_features {
+  float* vec;                    /* (E, 3) or NULL                  */
+  float* length;                 /* (E) or NULL                     */
+  float* sh;                     /* (E, (l_max + 1)^2) or NULL      */
+  float* bessel;                 /* (E, num_basis) or NULL          */
+  float* cutoff;                 /* (E) or NULL                     */
+  const float* bessel_weights;   /* (num_basis) device              */
+  int32_t l_max, integral_normalize, num_basis, cutoff_kind;
+  float r_max, cutoff_r_min, cutoff_r_max, cutoff_p, cutoff_eps;
+} eqt_edge_features;
+int eqt_radius_count(const eqt_radius_grid* grid, const float* pos, const int64_t* batch, int64_t n, float r, int32_t loop,
+                     int32_t max_neighbors, int32_t* degree, int32_t* status, void* stream);
+int eqt_radius_edges(const eqt_radius_grid* grid, const float* pos, const int64_t* batch, int64_t n, float r, int32_t loop,
+                     int32_t max_neighbors, const int64_t* ptr, int64_t* src, int64_t* dst, const eqt_edge_features* features,
+                     int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
