@@ -94,7 +94,67 @@ class TensorProductUVWDummy(Function):
         return g1, g2, gw, None, None, None
 
 
+#: largest per-call intermediate (N, num_Mij, C1, C2) of the 'uvw' product in bytes; larger batches are processed in
+#: slices of samples whose intermediate stays below it
+UVW_INTERMEDIATE_LIMIT = 1 << 30
+
+
+class TensorProductUVWChunked(Function):
+    """'uvw' product with weights shared by the batch, evaluated slice by slice over the samples.
+
+    The two-step chain materialises ``(N, num_Mij, C1, C2)`` - 1.6 MB per sample at l_max 3 and 64 channels - and
+    keeps it for the backward pass.  Here the forward pass runs the chain on slices of the batch and keeps
+    nothing but the inputs; the backward pass recomputes the intermediate of a slice, differentiates the slice
+    and adds up the weight gradient.  Memory is bounded by ``UVW_INTERMEDIATE_LIMIT`` whatever the batch size;
+    within a slice the contraction with the weights (K = C1 * C2 per path) and the weight gradient run on the
+    tensor-core paths of the indexed products."""
+
+    @staticmethod
+    def forward(ctx, input1, input2, weight, tp_info_forward, tp_info_backward1, tp_info_backward2, chunk):
+        infos = (tp_info_forward, tp_info_backward1, tp_info_backward2)
+        with torch.no_grad():
+            outs = [TensorProductUVWDummy.apply(input1[s:s + chunk], input2[s:s + chunk], weight, *infos)[0]
+                    for s in range(0, input1.shape[0], chunk)]
+        ctx.save_for_backward(input1, input2, weight)
+        ctx.infos, ctx.chunk = infos, chunk
+        return torch.cat(outs, dim=0)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, grad):
+        input1, input2, weight = ctx.saved_tensors
+        need = ctx.needs_input_grad[:3]
+        g1 = torch.empty_like(input1) if need[0] else None
+        g2 = torch.empty_like(input2) if need[1] else None
+        gw = torch.zeros_like(weight) if need[2] else None
+        for s in range(0, input1.shape[0], ctx.chunk):
+            sl = slice(s, s + ctx.chunk)
+            with torch.enable_grad():
+                a = input1[sl].detach().requires_grad_(need[0])
+                b = input2[sl].detach().requires_grad_(need[1])
+                # the reference's backward needs a weight that requires grad (it saves the intermediate only then)
+                w = weight.detach().requires_grad_(True)
+                out = TensorProductUVWDummy.apply(a, b, w, *ctx.infos)[0]
+                wanted = [t for t, n in zip((a, b, w), need) if n]
+                got = iter(torch.autograd.grad(out, wanted, grad[sl]))
+            if need[0]:
+                g1[sl] = next(got)
+            if need[1]:
+                g2[sl] = next(got)
+            if need[2]:
+                gw += next(got)
+        return g1, g2, gw, None, None, None, None
+
+
 def tensor_product_uvw(input1, input2, weight, tp_info_forward, tp_info_backward1=None, tp_info_backward2=None):
+    if weight.ndim == 4 and input1.ndim == 3 and input2.ndim == 3 and input1.shape[0] == input2.shape[0]:
+        per_sample = (tp_info_forward.info_Mij_fwd.out_size * input1.shape[-1] * input2.shape[-1] * input1.element_size())
+        if per_sample * input1.shape[0] > UVW_INTERMEDIATE_LIMIT:
+            chunk = max(1, UVW_INTERMEDIATE_LIMIT // per_sample)
+            if chunk >= 512:
+                chunk = chunk // 512 * 512           # whole tiles for the tensor-core paths
+            return TensorProductUVWChunked.apply(input1, input2, weight, tp_info_forward, tp_info_backward1,
+                                                 tp_info_backward2, chunk)
     return TensorProductUVWDummy.apply(input1, input2, weight, tp_info_forward, tp_info_backward1, tp_info_backward2)[0]
 
 

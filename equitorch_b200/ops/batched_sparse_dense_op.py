@@ -119,6 +119,10 @@ def sparse_product(op: int, input1: Tensor, input2: Optional[Tensor], scale=None
     elif out is None and op == _lib.OP_OUTER and not shared1 and not shared2 \
             and _tc.outer_supported(x, y, gather_index, index_out, out_accumulated, out_size, num_out):
         return _tc.outer_tc(x, y, scale, index1, index2, seg, num_out)
+    elif out is None and op == _lib.OP_OUTER and not shared1 and not shared2 \
+            and _tc.outer_supported(y, x, gather_index, index_out, out_accumulated, out_size, num_out):
+        # second operand wider than one tile (e.g. a flattened C1 * C2 intermediate): swap the roles, transpose back
+        return _tc.outer_tc(y, x, scale, index2, index1, seg, num_out).transpose(-1, -2).contiguous()
 
     tail = {_lib.OP_OUTER: (c1, c2), _lib.OP_INNER: (), _lib.OP_VECMAT: (c2,)}.get(op, (c1,))
     lead = (out_size,) if out_accumulated else (n, out_size)

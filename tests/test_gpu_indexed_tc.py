@@ -102,3 +102,35 @@ def test_layers_reach_tensor_cores_and_match_table_driven_kernels(monkeypatch):
         monkeypatch.setattr(tc, "MIN_BATCH", 512)
         for u, v in [(out, ref), *zip(grads, ref_grads)]:
             assert _rel(u, v) < 1e-5, name
+
+
+def test_tensor_product_uvw_sliced_over_samples(monkeypatch):
+    """TensorProduct 'uvw' (both operands channelled, 32 x 32 -> 32 channels, l_max 2) with the intermediate limit
+    lowered so that the batch is processed in slices: output and all three gradients against the float64 oracle
+    (dense path form) and against the unsliced chain; bound 1e-5."""
+    from equitorch_b200.nn.functional import tensor_products as ftp
+    ir, n, c = "0e+1o+2e", 1536, 32
+    g = torch.Generator().manual_seed(2)
+    layer = enn.TensorProduct(ir, ir, ir, c, c, c, internal_weights=False, feature_mode="uvw").to(DEV)
+    x1, x2 = torch.randn(n, 9, c, generator=g), torch.randn(n, 9, c, generator=g)
+    w = torch.randn(*layer.weight_shape, generator=g) / c
+    cot = torch.randn(n, 9, c, generator=g)
+    a, b, ww = (t.to(DEV).requires_grad_(True) for t in (x1, x2, w))
+    whole = layer(a, b, ww)
+    gwhole = torch.autograd.grad(whole, [a, b, ww], cot.to(DEV))
+    monkeypatch.setattr(ftp, "UVW_INTERMEDIATE_LIMIT", 512 * 35 * c * c * 4)       # slices of 512 samples
+    sliced = layer(a, b, ww)
+    gsliced = torch.autograd.grad(sliced, [a, b, ww], cot.to(DEV))
+    check_status()
+    for u, v in [(sliced, whole), *zip(gsliced, gwhole)]:
+        assert _rel(u, v) < 1e-5
+    m = 256                                                                      # oracle on the first samples
+    ao, bo, wo = x1[:m].double().requires_grad_(True), x2[:m].double().requires_grad_(True), w.double().requires_grad_(True)
+    ref = otp.tensor_product_dense(ao, bo, wo, ir, ir, ir, feature_mode="uvw")
+    assert _rel(sliced[:m], ref) < 1e-5
+    cot0 = cot.clone()
+    cot0[m:] = 0
+    gx1, gx2, gw = torch.autograd.grad(layer(a, b, ww), [a, b, ww], cot0.to(DEV))
+    ro = torch.autograd.grad(ref, [ao, bo, wo], cot[:m].double())
+    for u, v in zip((gx1[:m], gx2[:m], gw), ro):
+        assert _rel(u, v) < 1e-5
