@@ -132,6 +132,113 @@ def outer_order(s: Structure) -> np.ndarray:
     return out
 
 
+class TcPlan(NamedTuple):
+    """Layout of a structure for the tensor-core segment-sum kernel (16 x 16 components, 64 channels).
+
+    The per-node outer product Q[f, m_y] = sum_e x_e[f] y_e[m_y] (f = (m_feat, channel), 1024 features) is eight
+    tcgen05 tiles of 128 features.  A thread of the contraction stage reads one TMEM lane of every tile, i.e. one
+    channel of eight components m_feat; the components are dealt to the two lane halves so that every irrep of
+    the channelled operand lies in one half, and with it every intermediate row: ``mlist[h][i]`` is the component
+    held by tile ``i`` for the lanes of half ``h``."""
+    mlist: List[List[int]]                 # [2][8]
+    phases: List[List[dict]]               # per half: phases {tiles: [(i, cols kept)], rows: [(row, [(t, tile, m_y)])]}
+
+
+def _groups(keys: np.ndarray, row: np.ndarray, size: int) -> List[List[int]]:
+    """Components that share a row are one group (for irreps tables: the irreps)."""
+    parent = list(range(size))
+
+    def find(c):
+        while parent[c] != c:
+            parent[c] = parent[parent[c]]
+            c = parent[c]
+        return c
+    for r in np.unique(row):
+        ks = keys[row == r]
+        for k in ks[1:]:
+            a, b = find(int(ks[0])), find(int(k))
+            if a != b:
+                parent[max(a, b)] = min(a, b)
+    out = {}
+    for c in range(size):
+        out.setdefault(find(c), []).append(c)
+    return [sorted(v) for _, v in sorted(out.items())]
+
+
+def tc_plan(s: Structure):
+    if s.d_feat != 16 or s.d_y != 16:
+        return None
+    fgroups, ygroups = _groups(s.mf, s.row, s.d_feat), _groups(s.my, s.row, s.d_y)
+    # split the groups of the channelled operand into two halves of exactly eight components
+    import itertools
+    halves = None
+    for pick in range(1, len(fgroups)):
+        for combo in itertools.combinations(range(len(fgroups)), pick):
+            if sum(len(fgroups[g]) for g in combo) == 8:
+                halves = (list(combo), [g for g in range(len(fgroups)) if g not in combo])
+                break
+        if halves:
+            break
+    if halves is None:
+        return None
+    group_of_f = {m: g for g, ms in enumerate(fgroups) for m in ms}
+    group_of_y = {k: g for g, ks in enumerate(ygroups) for k in ks}
+    mlist, phases = [], []
+    for h in range(2):
+        ms = [m for g in halves[h] for m in fgroups[g]]
+        tile_of = {m: i for i, m in enumerate(ms)}
+        mlist.append(ms)
+        ph = []
+        for g in halves[h]:
+            for yg in range(len(ygroups)):
+                rows = {}
+                for t in range(len(s.row)):
+                    if group_of_f[int(s.mf[t])] == g and group_of_y[int(s.my[t])] == yg:
+                        rows.setdefault(int(s.row[t]), []).append((t, tile_of[int(s.mf[t])], int(s.my[t])))
+                if rows:
+                    ph.append(dict(tiles=[tile_of[m] for m in fgroups[g]], cols=list(ygroups[yg]), rows=sorted(rows.items())))
+        phases.append(ph)
+    return TcPlan(mlist, phases)
+
+
+def _emit_tc(s: Structure, plan: TcPlan) -> List[str]:
+    out = ["  // tensor-core segment sum: component of the channelled operand held by tile i for the lanes of half h",
+           "  static constexpr bool HAS_TC = true;",
+           "  __device__ __forceinline__ static int tc_mfeat(int h, int i) {",
+           "    switch (i) {"]
+    for i in range(8):
+        out.append(f"      case {i}: return h ? {plan.mlist[1][i]} : {plan.mlist[0][i]};")
+    out += ["      default: return 0;", "    }", "  }"]
+    used = set(int(r) for r in s.row)
+    for h in range(2):
+        out.append("  // contraction of one node by a lane of half %d: tq = TMEM address of the lane's row of tile 0 (tiles 16 columns apart)," % h)
+        out.append("  // sc = scales in shared memory (table order), o = the lane's channel of the node's first row (row stride C floats)")
+        out.append(f"  template <int C> __device__ __forceinline__ static void tc_node_h{h}(uint32_t tq, const float* sc, float* o) {{")
+        out.append("    float t16[16];")
+        for pi, ph in enumerate(plan.phases[h]):
+            cols = ph["cols"]
+            out.append("    {")
+            for i in ph["tiles"]:
+                out.append(f"      float q{i}[{len(cols)}];")
+                out.append(f"      tmem_ld16(tq + {16 * i}, t16);")
+                for n, k in enumerate(cols):
+                    out.append(f"      q{i}[{n}] = t16[{k}];")
+            for r, ents in ph["rows"]:
+                terms = [f"sc[{t}] * q{tile}[{cols.index(k)}]" for t, tile, k in ents]
+                expr = terms[0]
+                for term in terms[1:]:
+                    a, b = term.split(" * ")
+                    expr = f"fmaf({a}, {b}, {expr})"
+                out.append(f"      o[{r} * C] = {expr};")
+            out.append("    }")
+        if h == 0:
+            for r in range(s.num_rows):
+                if r not in used:
+                    out.append(f"    o[{r} * C] = 0.f;")
+        out.append("  }")
+    return out
+
+
 def _emit_outer_role(s: Structure, plan: OuterPlan, w: int) -> List[str]:
     """Functions of warp role ``w``.  A lane holds CPL channels; ``xr`` points at its channels of the
     staged feature row (component stride C floats), loaded component by component just before use."""
@@ -228,6 +335,11 @@ def emit_spec(idx: int, s: Structure, note: str) -> str:
            "  static constexpr int " + ", ".join(f"OT{w} = {o}" for w, o in enumerate(plan.offsets)) + ";"]
     for w in range(NUM_ROLES):
         out += _emit_outer_role(s, plan, w)
+    tcp = tc_plan(s)
+    if tcp is not None:
+        out += _emit_tc(s, tcp)
+    else:
+        out.append("  static constexpr bool HAS_TC = false;")
     out.append("};")
     return "\n".join(out)
 

@@ -22,11 +22,25 @@
 //    H[cell] = sum_t scale[t] G_d[row(t)] once per node, then a dense dot product per edge.
 //  * "generic": table-driven, one thread per output element; any structure, any channel count.
 #include <algorithm>
+#include <cstdlib>
 
-#include "common.cuh"
+#include "tc_common.cuh"
 
 namespace eqt {
 namespace specs {
+// 16 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
 template <int CPL> __device__ __forceinline__ void ld_lane(float (&x)[CPL], const float* p) {
   if constexpr (CPL == 2) { const float2 v = *reinterpret_cast<const float2*>(p); x[0] = v.x; x[1] = v.y; }
   else x[0] = p[0];
@@ -443,6 +457,303 @@ __global__ void __launch_bounds__(128 * CG, CG == 1 ? 3 : 1) tp_inner_spec_kerne
   }
 }
 
+
+// ---- tensor-core segment sum -----------------------------------------------------------------------------------
+// S[d, r, c] = sum_t scale[t] Q_d[m_y(t), m_feat(t), c]  with  Q_d = sum_{e -> d} y_e (x) x_e  as above, but the outer
+// product - 234 of every 240 multiply-adds of the step - runs on tcgen05: per node it is the GEMM
+//
+//     Q_d[f, m_y] = sum_e X[e, f] Y[e, m_y],      f = (m_feat, channel): 1024 features = 8 tiles of M = 128, N = 16,
+//
+// whose reduction index is the edge.  Edges are taken eight at a time (one MMA k-step; the last group of a node is
+// padded with zero rows), float32 operands are split into TF32 big / small parts (three MMAs per tile and group),
+// and the eight accumulators of a node (128 columns) are double buffered in tensor memory.
+//
+// One persistent CTA per SM, 14 warps:
+//   warp 0        producer: bulk copies of the gathered feature rows of a group (8 x 4 KB) into a 4-slot ring, the
+//                 harmonics rows by 16-byte cp.async
+//   warp 1        TMEM allocation, MMA issue (24 MMAs per group), tcgen05.commit towards splitters and contraction
+//   warps 2-5,    two splitter groups taking alternate edge groups: a thread owns one TMEM lane = one (component,
+//   warps 6-9     channel) of every tile, reads its eight edges' values from the ring, splits them and stores big /
+//                 small into the group's A slot in tensor memory (the MMAs read A from TMEM, so the features cross
+//                 shared memory once); one thread per harmonics value writes the two small B tiles
+//   warps 10-13   contraction: tcgen05.ld of the finished accumulator, the 353-entry CG contraction in registers
+//                 (unrolled at build time, every row produced by one lane), coalesced stores of S
+// All waits are bounded; on expiry the abort flag is raised, every role leaves its loop, TMEM is freed and the
+// status word is set.
+namespace segtc {
+
+constexpr int THREADS = 14 * 32;
+constexpr int GE = 8;                  // edges per group (one tf32 MMA k-step)
+constexpr int NS = 4;                  // ring slots
+constexpr int ROWF = 1024;             // floats per gathered row (16 components x 64 channels)
+constexpr int NODES_PER_CHUNK = 16;
+constexpr uint32_t TMEM_COLS = 512;    // 2 x 128 accumulators + 2 x 128 A slots
+constexpr uint32_t COL_A = 256;
+
+struct Shared {
+  uint64_t full[NS], empty[NS], a_ready[2], a_free[2], q_full[2], q_free[2];
+  uint32_t tmem_slot;
+  int abort_flag;
+};
+
+// layout of dynamic shared memory (1024-byte aligned): ring of raw rows, raw harmonics per slot, B tiles per A slot, scales
+constexpr size_t XS_BYTES = (size_t)NS * GE * ROWF * 4;            // 128 KB
+constexpr size_t YS_BYTES = (size_t)NS * GE * 16 * 4;              // 2 KB
+constexpr size_t YB_BYTES = 2 * 2 * 2048;                          // [A slot][big, small] 16 rows x 128 B
+constexpr size_t OFF_YS = XS_BYTES, OFF_YB = OFF_YS + YS_BYTES, OFF_SC = OFF_YB + YB_BYTES;
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const float (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15]))
+      : "memory");
+}
+
+// The node walk every role performs: nodes come in chunks of NODES_PER_CHUNK dealt round-robin to the CTAs.
+struct Walk {
+  const int64_t* ptr;
+  int64_t n_out;
+  int64_t chunk;        // current chunk
+  int d_in;             // next node inside the chunk
+  __device__ Walk(const FusedArgs& a) : ptr(a.ptr), n_out(a.n_out), chunk(blockIdx.x), d_in(0) {}
+  // next node of this CTA: returns false at the end; d = node, e0 = its first edge, deg = its edge count
+  __device__ bool next(int64_t& d, int64_t& e0, int& deg) {
+    for (;;) {
+      d = chunk * NODES_PER_CHUNK + d_in;
+      if (d_in < NODES_PER_CHUNK && d < n_out) break;
+      chunk += gridDim.x;
+      d_in = 0;
+      if (chunk * NODES_PER_CHUNK >= n_out) return false;
+    }
+    ++d_in;
+    e0 = __ldg(ptr + d);
+    deg = (int)(__ldg(ptr + d + 1) - e0);
+    return true;
+  }
+};
+
+}  // namespace segtc
+
+template <class S>
+__global__ void __launch_bounds__(segtc::THREADS, 1) tp_segsum_tc_kernel(FusedArgs a) {
+  using namespace segtc;
+  using namespace tc;
+  constexpr int C = 64;
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ Shared sh;
+  unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* xs = reinterpret_cast<float*>(base);
+  float* ys = reinterpret_cast<float*>(base + OFF_YS);
+  unsigned char* yb = base + OFF_YB;
+  float* ssc = reinterpret_cast<float*>(base + OFF_SC);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  for (int t = tid; t < S::T; t += THREADS) ssc[t] = __ldg(a.scale + t);
+  if (tid == 0) {
+    sh.abort_flag = 0;
+    for (int i = 0; i < NS; ++i) {
+      bar_init(&sh.full[i], 1 + 32);       // expect_tx arrival + one cp.async arrival per producer lane
+      bar_init(&sh.empty[i], 4);
+    }
+    for (int i = 0; i < 2; ++i) {
+      bar_init(&sh.a_ready[i], 4);
+      bar_init(&sh.a_free[i], 1);
+      bar_init(&sh.q_full[i], 1);
+      bar_init(&sh.q_free[i], 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(&sh.tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sh.tmem_slot;
+  volatile int* ab = &sh.abort_flag;
+
+  if (warp == 0) {
+    // ---------------- producer ----------------
+    Walk w(a);
+    int64_t d, e0;
+    int deg;
+    int g = 0;                                       // edge groups issued
+    while (!*ab && w.next(d, e0, deg)) {
+      for (int k0 = 0; k0 < deg; k0 += GE, ++g) {
+        const int cnt = min(GE, deg - k0), slot = g % NS;
+        // gather indices of the group, one edge per lane
+        int64_t fi = 0, yi = 0;
+        if (lane < cnt) {
+          const int64_t e = e0 + k0 + lane;
+          fi = a.fidx ? __ldg(a.fidx + e) : e;
+          yi = a.yidx ? __ldg(a.yidx + e) : e;
+        }
+        if (g >= NS) {
+          int ok = lane == 0 ? (int)bar_wait(&sh.empty[slot], (uint32_t)(((g / NS) - 1) & 1), ab) : 1;
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) break;
+        }
+        if (lane == 0) bar_expect_tx(&sh.full[slot], (uint32_t)cnt * ROWF * 4);
+        __syncwarp();
+        if (lane < cnt) bulk_load(xs + (size_t)(slot * GE + lane) * ROWF, a.feat + fi * ROWF, ROWF * 4, &sh.full[slot]);
+        // harmonics: lane = (edge, 16-byte chunk)
+        {
+          const int ed = lane >> 2, ch = lane & 3;
+          const int64_t yrow = __shfl_sync(0xffffffffu, yi, ed);
+          if (ed < cnt)
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_addr(ys + (slot * GE + ed) * 16 + ch * 4)),
+                         "l"(a.y + yrow * 16 + ch * 4) : "memory");
+        }
+        cp_async_arrive(&sh.full[slot]);
+      }
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_tf32(16);
+      Walk w(a);
+      int64_t d, e0;
+      int deg, g = 0, nq = 0;
+      bool ok = true;
+      while (ok && !*ab && w.next(d, e0, deg)) {
+        if (deg == 0) continue;
+        const int qb = nq & 1;
+        if (nq >= 2 && !bar_wait(&sh.q_free[qb], (uint32_t)(((nq >> 1) - 1) & 1), ab)) break;
+        tc_fence_after();
+        const uint32_t dq = tmem + (uint32_t)(qb * 128);
+        for (int k0 = 0; k0 < deg; k0 += GE, ++g) {
+          const int G = g & 1;
+          if (!bar_wait(&sh.a_ready[G], (uint32_t)((g >> 1) & 1), ab)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t bb = umma_desc(s32(yb + G * 4096)), bs = umma_desc(s32(yb + G * 4096 + 2048));
+          const uint32_t ta = tmem + COL_A + (uint32_t)(G * 128);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            umma_tf32_ta(dq + i * 16, ta + i * 16, bb, idesc, k0 != 0);
+            umma_tf32_ta(dq + i * 16, ta + i * 16, bs, idesc, 1);
+            umma_tf32_ta(dq + i * 16, ta + i * 16 + 8, bb, idesc, 1);
+          }
+          umma_commit(&sh.a_free[G]);               // the A slot and its B tiles may be rewritten once these MMAs are done
+        }
+        if (!ok) break;
+        umma_commit(&sh.q_full[qb]);
+        ++nq;
+      }
+    }
+  } else if (warp < 10) {
+    // ---------------- splitters ----------------
+    const int G = (warp - 2) >> 2, quarter = warp & 3;      // warps 2-5: group 0, 6-9: group 1; TMEM lanes 32 * (warp % 4)
+    const int L = quarter * 32 + lane, h = L >> 6, c = L & 63;
+    const int t128 = ((warp - 2) & 3) * 32 + lane;           // thread index inside the group: one harmonics value each
+    int fo[8];                                               // offset of this lane's feature inside a row, per tile
+#pragma unroll
+    for (int i = 0; i < 8; ++i) fo[i] = S::tc_mfeat(h, i) * C + c;
+    Walk w(a);
+    int64_t d, e0;
+    int deg, g = 0;
+    bool ok = true;
+    while (ok && !*ab && w.next(d, e0, deg)) {
+      for (int k0 = 0; k0 < deg; k0 += GE, ++g) {
+        if ((g & 1) != G) continue;
+        const int cnt = min(GE, deg - k0), slot = g % NS, u = g >> 1;
+        if (!bar_wait(&sh.full[slot], (uint32_t)((g / NS) & 1), ab)) { ok = false; break; }
+        if (u >= 1 && !bar_wait(&sh.a_free[G], (uint32_t)((u - 1) & 1), ab)) { ok = false; break; }
+        tc_fence_after();
+        const float* xr = xs + (size_t)slot * GE * ROWF;
+        const uint32_t ta = tmem + ((uint32_t)(quarter * 32) << 16) + COL_A + (uint32_t)(G * 128);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float v[16];
+#pragma unroll
+          for (int e = 0; e < GE; ++e) {
+            const float x = e < cnt ? xr[e * ROWF + fo[i]] : 0.f;
+            const float hi = rn_tf32(x);
+            v[e] = hi;
+            v[8 + e] = x - hi;
+          }
+          tmem_st16(ta + i * 16, v);
+        }
+        {   // harmonics value (edge, component) -> the two B tiles (128-byte rows, 16-byte chunks swizzled by the row)
+          const int ed = t128 >> 4, m = t128 & 15;
+          const float yv = ed < cnt ? ys[(slot * GE + ed) * 16 + m] : 0.f;
+          const float hi = rn_tf32(yv);
+          const uint32_t off = m * 128 + ((((uint32_t)ed >> 2) ^ (m & 7)) << 4) + (ed & 3) * 4;
+          *reinterpret_cast<float*>(yb + G * 4096 + off) = hi;
+          *reinterpret_cast<float*>(yb + G * 4096 + 2048 + off) = yv - hi;
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // B tiles: generic writes -> visible to the MMA
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          bar_arrive(&sh.a_ready[G]);
+          bar_arrive(&sh.empty[slot]);
+        }
+      }
+    }
+  } else {
+    // ---------------- contraction ----------------
+    const int quarter = warp & 3;                            // warps 10-13 -> 2, 3, 0, 1: every quarter once
+    const int L = quarter * 32 + lane, h = L >> 6, c = L & 63;
+    Walk w(a);
+    int64_t d, e0;
+    int deg, nq = 0;
+    while (!*ab && w.next(d, e0, deg)) {
+      float* o = a.out + d * (int64_t)(S::R * C) + c;
+      if (deg == 0) {                                        // node without edges: zero rows (each lane half its rows)
+        for (int r = h; r < S::R; r += 2) o[r * C] = 0.f;
+        continue;
+      }
+      const int qb = nq & 1;
+      if (!bar_wait(&sh.q_full[qb], (uint32_t)((nq >> 1) & 1), ab)) break;
+      tc_fence_after();
+      const uint32_t tq = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(qb * 128);
+      if (h == 0) S::template tc_node_h0<C>(tq, ssc, o);
+      else S::template tc_node_h1<C>(tq, ssc, o);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) bar_arrive(&sh.q_free[qb]);
+      ++nq;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+  }
+  if (sh.abort_flag) {
+    if (tid == 0) atomicExch(a.status, 1);
+    // copies that may still be in flight get a bounded chance to land before shared memory is released
+    if (tid == 0)
+      for (int i = 0; i < NS; ++i)
+        for (int ph = 0; ph < 2; ++ph)
+          for (int k = 0; k < 1024 && !bar_try(&sh.full[i], ph); ++k) __nanosleep(256);
+  }
+}
+
+template <class S>
+int launch_segsum_tc(const FusedArgs& a, cudaStream_t s) {
+  if constexpr (S::HAS_TC) {
+    constexpr size_t bytes = segtc::OFF_SC + sizeof(float) * ((S::T + 3) & ~3) + 1024;
+    auto kern = tp_segsum_tc_kernel<S>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) return fail(EQT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    const int64_t chunks = ceil_div(a.n_out, segtc::NODES_PER_CHUNK);
+    kern<<<(unsigned)std::min<int64_t>(chunks, sm_count()), segtc::THREADS, bytes, s>>>(a);
+    return check_launch("tp_segsum_tc_kernel");
+  } else {
+    return -1;
+  }
+}
+
 // ---- generic kernels ---------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) tp_segsum_generic_kernel(FusedArgs a) {
   const int64_t total = a.n_out * a.R * a.C;
@@ -506,9 +817,20 @@ int launch_spec(bool inner, const FusedArgs& a, cudaStream_t s) {
   return check_launch(inner ? "tp_inner_spec_kernel" : "tp_segsum_spec_kernel");
 }
 
+// the tensor-core kernel pays when nodes have several edges each (groups of eight) and everything is 16-byte aligned
+inline bool segsum_tc_wanted(const FusedArgs& a) {
+  static const bool enabled = [] { const char* v = getenv("EQT_SEGSUM_TC"); return !(v && v[0] == '0'); }();
+  return enabled && a.ptr && a.C == 64 && a.n_edges >= 4 * a.n_out && (reinterpret_cast<uintptr_t>(a.y) & 15u) == 0 &&
+         (reinterpret_cast<uintptr_t>(a.out) & 15u) == 0;
+}
+
 template <class S>
 bool try_spec(uint64_t key, bool inner, const FusedArgs& a, cudaStream_t s, int& rc) {
   if (key != S::KEY || a.T != S::T || a.R != S::R || a.DF != S::DF || a.DY != S::DY) return false;
+  if (!inner && S::HAS_TC && segsum_tc_wanted(a)) {
+    rc = launch_segsum_tc<S>(a, s);
+    if (rc >= 0) return true;
+  }
   if (a.C == 128) { rc = launch_spec<S, 2, 2>(inner, a, s); return true; }
   if (a.C == 64) { rc = launch_spec<S, 2, 1>(inner, a, s); return true; }
   if (a.C == 32) { rc = launch_spec<S, 1, 1>(inner, a, s); return true; }
