@@ -1,7 +1,7 @@
 """Benchmark of the hot path: edges/s of the Clebsch-Gordan tensor-product layer, forward + backward
 (l_max = 3, 64 channels, full 64 -> 64 channel mixing per path), on N GPUs of one box.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg5|cfg5q|cfg2|cfg1|cfg3|cfg4|epilogue]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg5|cfg5q|cfg2|cfg1|cfg3|cfg4|featurize|epilogue]
                     [--feature-mode uv|uu] [--repeats R] [--impl ours|reference|reference_triton] [--no-graph] [--no-cpu-baseline]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
@@ -21,6 +21,8 @@ Workloads (seeded synthetic data, shapes of the benchmark configurations):
   cfg1 / cfg3 / cfg4  the small configurations (equitorch_b200/utils/workloads.py), one GPU, their own JSON
         lines: per-sample 'uu' product at l_max 2; molecular-style layer with per-edge bfloat16 weights;
         Wigner-rotated SO(2) linear layer at l = 0..6.  L2 is flushed between steps.
+  featurize  side measurement, one GPU: radius graph + edge vectors + harmonics + Bessel basis + cutoff of the
+        scaling graph's point cloud (100k points, ~2M edges) in two kernel passes.
   epilogue  side measurement, one GPU: Gate -> BatchRMSNorm -> LayerRMSNorm forward + backward on 100k x 16 x 64
         node features (its own JSON line; not the metric of the benchmark).
 
@@ -460,7 +462,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="cfg5", choices=["cfg5", "cfg2", "cfg5q", "cfg1", "cfg3", "cfg4", "epilogue"])
+    ap.add_argument("--workload", default="cfg5", choices=["cfg5", "cfg2", "cfg5q", "cfg1", "cfg3", "cfg4", "featurize", "epilogue"])
     ap.add_argument("--feature-mode", default="uv", choices=["uv", "uu"],
                     help="uv: 64 x 64 channel mixing per path (the metric); uu: channel-wise weights per path")
     ap.add_argument("--repeats", type=int, default=5, help="how often the timed region of K steps is repeated (median reported)")
@@ -474,7 +476,7 @@ def main():
         return run_reference_triton(args)
     if args.workload == "epilogue":
         return run_epilogue(args)
-    if args.workload in ("cfg1", "cfg3", "cfg4"):
+    if args.workload in ("cfg1", "cfg3", "cfg4", "featurize"):
         return run_small(args)
 
     import torch.distributed as dist

@@ -214,21 +214,26 @@ def _emit_tc(s: Structure, plan: TcPlan) -> List[str]:
         out.append("  // contraction of one node by a lane of half %d: tq = TMEM address of the lane's row of tile 0 (tiles 16 columns apart)," % h)
         out.append("  // sc = scales in shared memory (table order), o = the lane's channel of the node's first row (row stride C floats)")
         out.append(f"  template <int C> __device__ __forceinline__ static void tc_node_h{h}(uint32_t tq, const float* sc, float* o) {{")
-        out.append("    float t16[16];")
         for pi, ph in enumerate(plan.phases[h]):
             cols = ph["cols"]
+            # smallest power-of-two run of columns covering the phase's components; all tiles are requested before one wait
+            lo, width = min(cols), 1
+            while lo + width <= max(cols):
+                width *= 2
+            if lo + width > 16:
+                lo = 16 - width
             out.append("    {")
             for i in ph["tiles"]:
-                out.append(f"      float q{i}[{len(cols)}];")
-                out.append(f"      tmem_ld16(tq + {16 * i}, t16);")
-                for n, k in enumerate(cols):
-                    out.append(f"      q{i}[{n}] = t16[{k}];")
+                out.append(f"      uint32_t q{i}[{width}];")
+                out.append(f"      tmem_ld_nowait<{width}>(tq + {16 * i + lo}, q{i});")
+            out.append("      tmem_wait_ld();")
+            for i in ph["tiles"]:
+                out.append(f"      tmem_touch<{width}>(q{i});")
             for r, ents in ph["rows"]:
-                terms = [f"sc[{t}] * q{tile}[{cols.index(k)}]" for t, tile, k in ents]
-                expr = terms[0]
-                for term in terms[1:]:
-                    a, b = term.split(" * ")
-                    expr = f"fmaf({a}, {b}, {expr})"
+                terms = [(f"sc[{t}]", f"__uint_as_float(q{tile}[{k - lo}])") for t, tile, k in ents]
+                expr = f"{terms[0][0]} * {terms[0][1]}"
+                for a_, b_ in terms[1:]:
+                    expr = f"fmaf({a_}, {b_}, {expr})"
                 out.append(f"      o[{r} * C] = {expr};")
             out.append("    }")
         if h == 0:

@@ -28,18 +28,35 @@
 
 namespace eqt {
 namespace specs {
-// 16 columns of this thread's TMEM lane
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
-  uint32_t r[16];
+// N columns (1, 2, 4, 8 or 16) of this thread's TMEM lane, requested without waiting: several requests are followed by
+// one tmem_wait_ld(), and tmem_touch() on every array keeps its uses behind the wait
+template <int N> __device__ __forceinline__ void tmem_ld_nowait(uint32_t taddr, uint32_t (&r)[N]);
+template <> __device__ __forceinline__ void tmem_ld_nowait<1>(uint32_t taddr, uint32_t (&r)[1]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r[0]) : "r"(taddr) : "memory");
+}
+template <> __device__ __forceinline__ void tmem_ld_nowait<2>(uint32_t taddr, uint32_t (&r)[2]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(taddr) : "memory");
+}
+template <> __device__ __forceinline__ void tmem_ld_nowait<4>(uint32_t taddr, uint32_t (&r)[4]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(taddr) : "memory");
+}
+template <> __device__ __forceinline__ void tmem_ld_nowait<8>(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(taddr) : "memory");
+}
+template <> __device__ __forceinline__ void tmem_ld_nowait<16>(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr) : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void tmem_touch(uint32_t (&r)[N]) {
 #pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+  for (int i = 0; i < N; ++i) asm volatile("" : "+r"(r[i]) :: "memory");
 }
 template <int CPL> __device__ __forceinline__ void ld_lane(float (&x)[CPL], const float* p) {
   if constexpr (CPL == 2) { const float2 v = *reinterpret_cast<const float2*>(p); x[0] = v.x; x[1] = v.y; }
@@ -468,10 +485,11 @@ __global__ void __launch_bounds__(128 * CG, CG == 1 ? 3 : 1) tp_inner_spec_kerne
 // padded with zero rows), float32 operands are split into TF32 big / small parts (three MMAs per tile and group),
 // and the eight accumulators of a node (128 columns) are double buffered in tensor memory.
 //
-// One persistent CTA per SM, 14 warps:
+// One persistent CTA per SM, 15 warps:
 //   warp 0        producer: bulk copies of the gathered feature rows of a group (8 x 4 KB) into a 4-slot ring, the
 //                 harmonics rows by 16-byte cp.async
-//   warp 1        TMEM allocation, MMA issue (24 MMAs per group), tcgen05.commit towards splitters and contraction
+//   warps 1, 14   TMEM allocation (warp 1), MMA issue (12 of the 24 MMAs of a group each), tcgen05.commit towards
+//                 splitters and contraction
 //   warps 2-5,    two splitter groups taking alternate edge groups: a thread owns one TMEM lane = one (component,
 //   warps 6-9     channel) of every tile, reads its eight edges' values from the ring, splits them and stores big /
 //                 small into the group's A slot in tensor memory (the MMAs read A from TMEM, so the features cross
@@ -482,7 +500,7 @@ __global__ void __launch_bounds__(128 * CG, CG == 1 ? 3 : 1) tp_inner_spec_kerne
 // status word is set.
 namespace segtc {
 
-constexpr int THREADS = 14 * 32;
+constexpr int THREADS = 15 * 32;
 constexpr int GE = 8;                  // edges per group (one tf32 MMA k-step)
 constexpr int NS = 4;                  // ring slots
 constexpr int ROWF = 1024;             // floats per gathered row (16 components x 64 channels)
@@ -512,25 +530,34 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const float (&v)[16]) 
       : "memory");
 }
 
-// The node walk every role performs: nodes come in chunks of NODES_PER_CHUNK dealt round-robin to the CTAs.
+// The node walk every role performs: nodes come in chunks of NODES_PER_CHUNK dealt round-robin to the CTAs.  The
+// segment pointers are read two nodes ahead of their use, so the walk does not wait for a load per node.
 struct Walk {
   const int64_t* ptr;
-  int64_t n_out;
-  int64_t chunk;        // current chunk
+  int n_out;            // 32-bit state: the launcher checks that nodes and edges fit
+  int chunk;            // current chunk
   int d_in;             // next node inside the chunk
-  __device__ Walk(const FusedArgs& a) : ptr(a.ptr), n_out(a.n_out), chunk(blockIdx.x), d_in(0) {}
+  int p0, p1, p2;       // ptr[d], ptr[d + 1], ptr[d + 2] of the next node d
+  __device__ int at(int i) const { return (int)__ldg(ptr + min(i, n_out)); }
+  __device__ void prime() {
+    const int d = chunk * NODES_PER_CHUNK;
+    p0 = at(d); p1 = at(d + 1); p2 = at(d + 2);
+  }
+  __device__ Walk(const FusedArgs& a) : ptr(a.ptr), n_out((int)a.n_out), chunk(blockIdx.x), d_in(0) { prime(); }
   // next node of this CTA: returns false at the end; d = node, e0 = its first edge, deg = its edge count
-  __device__ bool next(int64_t& d, int64_t& e0, int& deg) {
-    for (;;) {
-      d = chunk * NODES_PER_CHUNK + d_in;
-      if (d_in < NODES_PER_CHUNK && d < n_out) break;
+  __device__ bool next(int& d, int& e0, int& deg) {
+    d = chunk * NODES_PER_CHUNK + d_in;
+    if (d_in >= NODES_PER_CHUNK || d >= n_out) {
       chunk += gridDim.x;
       d_in = 0;
-      if (chunk * NODES_PER_CHUNK >= n_out) return false;
+      d = chunk * NODES_PER_CHUNK;
+      if (d >= n_out) return false;
+      prime();
     }
     ++d_in;
-    e0 = __ldg(ptr + d);
-    deg = (int)(__ldg(ptr + d + 1) - e0);
+    e0 = p0;
+    deg = p1 - p0;
+    p0 = p1; p1 = p2; p2 = at(d + 3);
     return true;
   }
 };
@@ -560,8 +587,8 @@ __global__ void __launch_bounds__(segtc::THREADS, 1) tp_segsum_tc_kernel(FusedAr
     }
     for (int i = 0; i < 2; ++i) {
       bar_init(&sh.a_ready[i], 4);
-      bar_init(&sh.a_free[i], 1);
-      bar_init(&sh.q_full[i], 1);
+      bar_init(&sh.a_free[i], 2);          // one commit per MMA issuer
+      bar_init(&sh.q_full[i], 2);
       bar_init(&sh.q_free[i], 4);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -579,19 +606,26 @@ __global__ void __launch_bounds__(segtc::THREADS, 1) tp_segsum_tc_kernel(FusedAr
   if (warp == 0) {
     // ---------------- producer ----------------
     Walk w(a);
-    int64_t d, e0;
-    int deg;
+    int d, e0, deg;
     int g = 0;                                       // edge groups issued
+    // gather indices, one edge per lane, requested one group ahead: within a chunk the edges of consecutive nodes are
+    // consecutive, so the next group starts where this one ends (row numbers fit 32 bits: checked by the launcher)
+    int pf_e = -1, pf_f = 0, pf_y = 0;
+    auto fetch = [&](int first, int& f, int& y) {
+      const int e = first + lane;
+      const bool in = lane < GE && e < (int)a.n_edges;
+      f = in ? (a.fidx ? (int)__ldg(a.fidx + e) : e) : 0;
+      y = in ? (a.yidx ? (int)__ldg(a.yidx + e) : e) : 0;
+    };
     while (!*ab && w.next(d, e0, deg)) {
       for (int k0 = 0; k0 < deg; k0 += GE, ++g) {
         const int cnt = min(GE, deg - k0), slot = g % NS;
-        // gather indices of the group, one edge per lane
-        int64_t fi = 0, yi = 0;
-        if (lane < cnt) {
-          const int64_t e = e0 + k0 + lane;
-          fi = a.fidx ? __ldg(a.fidx + e) : e;
-          yi = a.yidx ? __ldg(a.yidx + e) : e;
-        }
+        const int eg = e0 + k0;
+        int fi, yi;
+        if (pf_e == eg) { fi = pf_f; yi = pf_y; }
+        else fetch(eg, fi, yi);
+        pf_e = eg + cnt;
+        fetch(pf_e, pf_f, pf_y);
         if (g >= NS) {
           int ok = lane == 0 ? (int)bar_wait(&sh.empty[slot], (uint32_t)(((g / NS) - 1) & 1), ab) : 1;
           ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -599,7 +633,7 @@ __global__ void __launch_bounds__(segtc::THREADS, 1) tp_segsum_tc_kernel(FusedAr
         }
         if (lane == 0) bar_expect_tx(&sh.full[slot], (uint32_t)cnt * ROWF * 4);
         __syncwarp();
-        if (lane < cnt) bulk_load(xs + (size_t)(slot * GE + lane) * ROWF, a.feat + fi * ROWF, ROWF * 4, &sh.full[slot]);
+        if (lane < cnt) bulk_load(xs + (size_t)(slot * GE + lane) * ROWF, a.feat + (int64_t)fi * ROWF, ROWF * 4, &sh.full[slot]);
         // harmonics: lane = (edge, 16-byte chunk)
         {
           const int ed = lane >> 2, ch = lane & 3;
@@ -612,13 +646,14 @@ __global__ void __launch_bounds__(segtc::THREADS, 1) tp_segsum_tc_kernel(FusedAr
       }
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
-  } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
+  } else if (warp == 1 || warp == 14) {
+    // ---------------- MMA issuers: warp 1 takes tiles 0-3, warp 14 tiles 4-7 (issue of 24 small MMAs per group from
+    // one thread was the longest serial chain of the kernel) ----------------
+    const int tile0 = warp == 1 ? 0 : 4;
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_tf32(16);
       Walk w(a);
-      int64_t d, e0;
-      int deg, g = 0, nq = 0;
+      int d, e0, deg, g = 0, nq = 0;
       bool ok = true;
       while (ok && !*ab && w.next(d, e0, deg)) {
         if (deg == 0) continue;
@@ -633,7 +668,8 @@ __global__ void __launch_bounds__(segtc::THREADS, 1) tp_segsum_tc_kernel(FusedAr
           const uint64_t bb = umma_desc(s32(yb + G * 4096)), bs = umma_desc(s32(yb + G * 4096 + 2048));
           const uint32_t ta = tmem + COL_A + (uint32_t)(G * 128);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
+          for (int j = 0; j < 4; ++j) {
+            const int i = tile0 + j;
             umma_tf32_ta(dq + i * 16, ta + i * 16, bb, idesc, k0 != 0);
             umma_tf32_ta(dq + i * 16, ta + i * 16, bs, idesc, 1);
             umma_tf32_ta(dq + i * 16, ta + i * 16 + 8, bb, idesc, 1);
@@ -654,8 +690,7 @@ __global__ void __launch_bounds__(segtc::THREADS, 1) tp_segsum_tc_kernel(FusedAr
 #pragma unroll
     for (int i = 0; i < 8; ++i) fo[i] = S::tc_mfeat(h, i) * C + c;
     Walk w(a);
-    int64_t d, e0;
-    int deg, g = 0;
+    int d, e0, deg, g = 0;
     bool ok = true;
     while (ok && !*ab && w.next(d, e0, deg)) {
       for (int k0 = 0; k0 < deg; k0 += GE, ++g) {
@@ -701,10 +736,9 @@ __global__ void __launch_bounds__(segtc::THREADS, 1) tp_segsum_tc_kernel(FusedAr
     const int quarter = warp & 3;                            // warps 10-13 -> 2, 3, 0, 1: every quarter once
     const int L = quarter * 32 + lane, h = L >> 6, c = L & 63;
     Walk w(a);
-    int64_t d, e0;
-    int deg, nq = 0;
+    int d, e0, deg, nq = 0;
     while (!*ab && w.next(d, e0, deg)) {
-      float* o = a.out + d * (int64_t)(S::R * C) + c;
+      float* o = a.out + (int64_t)d * (S::R * C) + c;
       if (deg == 0) {                                        // node without edges: zero rows (each lane half its rows)
         for (int r = h; r < S::R; r += 2) o[r * C] = 0.f;
         continue;
@@ -820,7 +854,7 @@ int launch_spec(bool inner, const FusedArgs& a, cudaStream_t s) {
 // the tensor-core kernel pays when nodes have several edges each (groups of eight) and everything is 16-byte aligned
 inline bool segsum_tc_wanted(const FusedArgs& a) {
   static const bool enabled = [] { const char* v = getenv("EQT_SEGSUM_TC"); return !(v && v[0] == '0'); }();
-  return enabled && a.ptr && a.C == 64 && a.n_edges >= 4 * a.n_out && (reinterpret_cast<uintptr_t>(a.y) & 15u) == 0 &&
+  return enabled && a.ptr && a.C == 64 && a.n_edges >= 4 * a.n_out && a.n_out < 0x7fffffffll && (reinterpret_cast<uintptr_t>(a.y) & 15u) == 0 &&
          (reinterpret_cast<uintptr_t>(a.out) & 15u) == 0;
 }
 

@@ -145,4 +145,25 @@ def cfg4(dev, edges: int = 100_000) -> Workload:
                     "31.4 KB/edge fused: x 6272 + angles 12 + out 6272 forward; g, x, gx 6272 each + 12 backward")
 
 
-BUILDERS = {"cfg1": cfg1, "cfg3": cfg3, "cfg4": cfg4}
+def featurize(dev, nodes: int = 100_000, box: float = 27.56, cutoff: float = 1.0) -> Workload:
+    """Edge featurisation of the scaling graph's point cloud: 100k points uniform in a cube of side 27.56, cutoff 1.0
+    (about 2M directed edges): radius graph + edge vectors + harmonics l_max 3 + 8 Bessel functions + polynomial
+    cutoff in two kernel passes (no gradient)."""
+    from .. import nn as enn
+    from ..transforms import EdgeFeaturizer
+    g = torch.Generator().manual_seed(0)
+    pos = torch.rand(nodes, 3, generator=g) * box
+    feat = EdgeFeaturizer(cutoff, 3, enn.BesselBasis(cutoff, 8).to(dev), enn.PolynomialCutoff(cutoff), max_num_neighbors=64)
+    pd = pos.to(dev)
+    edges = int(feat.features(pd).src.numel())
+
+    def step():
+        f = feat.features(pd)
+        return f.cutoff.sum().reshape(1), [f.ptr[-1:].float()]
+
+    return Workload(f"featurize: {nodes} points uniform in a cube of side {box}, cutoff {cutoff} ({edges} directed edges), harmonics "
+                    "l_max 3, 8 Bessel functions, polynomial cutoff", "edges", edges, "f32", 132.0, [_pin(pos)], [pd], step,
+                    "132 B written per edge: source and target 16, vector 12, length 4, harmonics 64, Bessel 32, cutoff 4")
+
+
+BUILDERS = {"cfg1": cfg1, "cfg3": cfg3, "cfg4": cfg4, "featurize": featurize}
