@@ -485,9 +485,9 @@ __global__ void __launch_bounds__(128 * CG, CG == 1 ? 3 : 1) tp_inner_spec_kerne
 // padded with zero rows), float32 operands are split into TF32 big / small parts (three MMAs per tile and group),
 // and the eight accumulators of a node (128 columns) are double buffered in tensor memory.
 //
-// One persistent CTA per SM, 15 warps:
-//   warp 0        producer: bulk copies of the gathered feature rows of a group (8 x 4 KB) into a 4-slot ring, the
-//                 harmonics rows by 16-byte cp.async
+// One persistent CTA per SM, 16 warps:
+//   warps 0, 15   producers: bulk copies of the gathered feature rows of a group (8 x 4 KB, four requests each) into a
+//                 4-slot ring, the harmonics rows by 16-byte cp.async (warp 0)
 //   warps 1, 14   TMEM allocation (warp 1), MMA issue (12 of the 24 MMAs of a group each), tcgen05.commit towards
 //                 splitters and contraction
 //   warps 2-5,    two splitter groups taking alternate edge groups: a thread owns one TMEM lane = one (component,
@@ -500,7 +500,7 @@ __global__ void __launch_bounds__(128 * CG, CG == 1 ? 3 : 1) tp_inner_spec_kerne
 // status word is set.
 namespace segtc {
 
-constexpr int THREADS = 15 * 32;
+constexpr int THREADS = 16 * 32;
 constexpr int GE = 8;                  // edges per group (one tf32 MMA k-step)
 constexpr int NS = 4;                  // ring slots
 constexpr int ROWF = 1024;             // floats per gathered row (16 components x 64 channels)
@@ -603,8 +603,10 @@ __global__ void __launch_bounds__(segtc::THREADS, 1) tp_segsum_tc_kernel(FusedAr
   const uint32_t tmem = sh.tmem_slot;
   volatile int* ab = &sh.abort_flag;
 
-  if (warp == 0) {
-    // ---------------- producer ----------------
+  if (warp == 0 || warp == 15) {
+    // ---------------- producers: warp 0 requests rows 0-3 of every group, the harmonics and arms the barrier; warp 15
+    // requests rows 4-7 (the issue of a bulk copy costs a few hundred cycles per request, so two warps share it) ----
+    const int row0 = warp == 0 ? 0 : GE / 2;
     Walk w(a);
     int d, e0, deg;
     int g = 0;                                       // edge groups issued
@@ -631,18 +633,19 @@ __global__ void __launch_bounds__(segtc::THREADS, 1) tp_segsum_tc_kernel(FusedAr
           ok = __shfl_sync(0xffffffffu, ok, 0);
           if (!ok) break;
         }
-        if (lane == 0) bar_expect_tx(&sh.full[slot], (uint32_t)cnt * ROWF * 4);
+        if (warp == 0 && lane == 0) bar_expect_tx(&sh.full[slot], (uint32_t)cnt * ROWF * 4);
         __syncwarp();
-        if (lane < cnt) bulk_load(xs + (size_t)(slot * GE + lane) * ROWF, a.feat + (int64_t)fi * ROWF, ROWF * 4, &sh.full[slot]);
-        // harmonics: lane = (edge, 16-byte chunk)
-        {
+        if (lane >= row0 && lane < row0 + GE / 2 && lane < cnt)
+          bulk_load(xs + (size_t)(slot * GE + lane) * ROWF, a.feat + (int64_t)fi * ROWF, ROWF * 4, &sh.full[slot]);
+        if (warp == 0) {
+          // harmonics: lane = (edge, 16-byte chunk)
           const int ed = lane >> 2, ch = lane & 3;
           const int64_t yrow = __shfl_sync(0xffffffffu, yi, ed);
           if (ed < cnt)
             asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_addr(ys + (slot * GE + ed) * 16 + ch * 4)),
                          "l"(a.y + yrow * 16 + ch * 4) : "memory");
+          cp_async_arrive(&sh.full[slot]);
         }
-        cp_async_arrive(&sh.full[slot]);
       }
     }
     asm volatile("cp.async.wait_all;" ::: "memory");
