@@ -57,6 +57,7 @@ struct MixLaunch {
   int stages;
   int tmem_cols;        // power of two >= 2 * max_cols (+ 64 per stage with a_in_tmem)
   int a_in_tmem;        // split A operand lives in tensor memory instead of shared memory
+  int issuers;          // MMA issuer warps (2 when two accumulators per tile fit tensor memory)
   int* status;
 };
 
@@ -107,11 +108,16 @@ int launch_jobs(const GemmJob* jobs, int count, int64_t n, int* status, cudaStre
         stage_bytes = sb;
       }
     }
+    L.issuers = 1;
+    if (L.a_in_tmem && 4 * L.max_cols + 64 * 4 <= 512) {      // two accumulators per tile and at least four A slots
+      L.issuers = 2;
+      L.stages = std::min(L.stages, (512 - 4 * L.max_cols) / 64);
+    }
     if (L.stages < 2) return fail(EQT_ERR_UNSUPPORTED, "tile too wide for the shared-memory ring");
     // the epilogue reads accumulators in groups of 32 columns, so the second one is padded to a multiple of 32
-    const int acc_cols = L.max_cols + (L.max_cols + 31) / 32 * 32;
+    const int acc_cols = (2 * L.issuers - 1) * L.max_cols + (L.max_cols + 31) / 32 * 32;
     L.tmem_cols = 32;
-    while (L.tmem_cols < std::max(acc_cols, 2 * L.max_cols + (L.a_in_tmem ? 64 * L.stages : 0))) L.tmem_cols <<= 1;
+    while (L.tmem_cols < std::max(acc_cols, 2 * L.issuers * L.max_cols + (L.a_in_tmem ? 64 * L.stages : 0))) L.tmem_cols <<= 1;
     int64_t total = 0;
     for (int q = 0; q < m; ++q) {
       const GemmJob& j = jobs[first + q];
@@ -136,7 +142,7 @@ int launch_jobs(const GemmJob* jobs, int count, int64_t n, int* status, cudaStre
     }
     L.total_tiles = total;
     const unsigned grid = (unsigned)std::min<int64_t>(total, sm_count());
-    mix_tc_kernel<<<grid, TC_THREADS, (size_t)L.stages * stage_bytes + 1024, st>>>(L);
+    mix_tc_kernel<<<grid, TC_THREADS + 32, (size_t)L.stages * stage_bytes + 1024, st>>>(L);
     if (int rc = check_launch("mix_tc_kernel")) return rc;
   }
   return EQT_OK;

@@ -670,13 +670,14 @@ __global__ void __launch_bounds__(segtc::THREADS, 1) tp_segsum_tc_kernel(FusedAr
           tc_fence_after();
           const uint64_t bb = umma_desc(s32(yb + G * 4096)), bs = umma_desc(s32(yb + G * 4096 + 2048));
           const uint32_t ta = tmem + COL_A + (uint32_t)(G * 128);
+          // MMAs into one accumulator execute one after the other, so the three products of a tile are issued four
+          // tiles apart instead of back to back
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int i = tile0 + j;
-            umma_tf32_ta(dq + i * 16, ta + i * 16, bb, idesc, k0 != 0);
-            umma_tf32_ta(dq + i * 16, ta + i * 16, bs, idesc, 1);
-            umma_tf32_ta(dq + i * 16, ta + i * 16 + 8, bb, idesc, 1);
-          }
+          for (int j = 0; j < 4; ++j) umma_tf32_ta(dq + (tile0 + j) * 16, ta + (tile0 + j) * 16, bb, idesc, k0 != 0);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) umma_tf32_ta(dq + (tile0 + j) * 16, ta + (tile0 + j) * 16, bs, idesc, 1);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) umma_tf32_ta(dq + (tile0 + j) * 16, ta + (tile0 + j) * 16 + 8, bb, idesc, 1);
           umma_commit(&sh.a_free[G]);               // the A slot and its B tiles may be rewritten once these MMAs are done
         }
         if (!ok) break;
