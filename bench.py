@@ -717,8 +717,8 @@ def main():
     # features of the profiling workload fit L2 and those of the full workload do not, so for the gathering
     # kernels the scaled figure is a lower bound.
     ncu_dram_bytes_cfg5q = {
-        "cg_segment_sum[fwd]": 201.3e6 + 582.9e6, "cg_segment_sum[grad_x]": 192.0e6 + 579.6e6,
-        "cg_inner[grad_y]": 796.2e6 + 34.5e6, "channel_mix[fwd]": 723.0e6, "channel_mix[grad_x]": 723.0e6,
+        "cg_segment_sum[fwd]": 181.1e6 + 577.5e6, "cg_segment_sum[grad_x]": 188.3e6 + 578.6e6,
+        "cg_inner[grad_y]": 796.4e6 + 33.2e6, "channel_mix[fwd]": 723.7e6, "channel_mix[grad_x]": 723.7e6,
     }
     if top:
         roofline = {"kernel": top, "bound": "hbm", "achieved": table[top]["algorithmic_GBps"], "peak": pk["hbm_gbs"],

@@ -60,14 +60,17 @@ class _SegmentSum(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad):
         ptr, perm = ctx.saved_tensors
-        node = torch.repeat_interleave(torch.arange(ptr.numel() - 1, device=ptr.device), ptr[1:] - ptr[:-1])
-        g = _gather_rows_raw(grad.contiguous(), node)            # gradient of the e-th summed row
+        # node of every summed position without a host round trip (the step stays capturable in a CUDA graph):
+        # position e lies in segment d when ptr[d] <= e < ptr[d+1]; positions outside [ptr[0], ptr[-1]) get zero
+        count = ctx.rows if perm is None else perm.shape[0]
+        nodes = ptr.numel() - 1
+        pos = torch.arange(count, device=ptr.device, dtype=ptr.dtype)
+        node = torch.searchsorted(ptr.contiguous(), pos, right=True) - 1
+        inside = (node >= 0) & (node < nodes)
+        g = _gather_rows_raw(grad.contiguous(), node.clamp_(0, max(nodes - 1, 0)))      # gradient of the e-th summed row
+        g = g * inside.view(-1, *([1] * (g.ndim - 1))).to(g.dtype)
         if perm is None:
-            if g.shape[0] == ctx.rows:
-                return g, None, None
-            out = torch.zeros(ctx.rows, *g.shape[1:], dtype=g.dtype, device=g.device)
-            out[int(ptr[0]):int(ptr[0]) + g.shape[0]] = g
-            return out, None, None
+            return g, None, None
         out = torch.zeros(ctx.rows, *g.shape[1:], dtype=g.dtype, device=g.device)
         return out.index_add_(0, perm, g), None, None
 

@@ -115,3 +115,28 @@ def test_gather_and_segment_sum():
     inv[perm] = torch.arange(edges)
     got2 = segment_sum(xe[perm], ptr.to(DEV), inv.to(DEV))
     torch.testing.assert_close(got2, got, rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("use_perm", [False, True])
+def test_segment_sum_gradient(use_perm):
+    """Gradient of the segment sum against index_add on float64, with rows before ptr[0] and after ptr[-1] that
+    belong to no segment (their gradient is zero)."""
+    g = torch.Generator().manual_seed(5)
+    nodes, edges, lead, trail = 37, 300, 5, 7
+    dst = torch.sort(torch.randint(0, nodes, (edges,), generator=g)).values
+    ptr = torch.zeros(nodes + 1, dtype=torch.long)
+    ptr[1:] = torch.cumsum(torch.bincount(dst, minlength=nodes), 0)
+    ptr += lead
+    rows = lead + edges + trail
+    x = torch.randn(rows, 4, 8, generator=g)
+    cot = torch.randn(nodes, 4, 8, generator=g)
+    perm = torch.randperm(rows, generator=g) if use_perm else None
+    xd = x.to(DEV).requires_grad_(True)
+    out = segment_sum(xd, ptr.to(DEV), None if perm is None else perm.to(DEV))
+    (gx,) = torch.autograd.grad(out, xd, cot.to(DEV))
+    xr = x.double().requires_grad_(True)
+    src_rows = xr if perm is None else xr[perm]
+    want = torch.zeros(nodes, 4, 8, dtype=torch.float64).index_add_(0, dst, src_rows[lead:lead + edges])
+    torch.testing.assert_close(out.double().cpu(), want.detach(), rtol=1e-5, atol=1e-5)
+    (gr,) = torch.autograd.grad(want, xr, cot.double())
+    torch.testing.assert_close(gx.double().cpu(), gr, rtol=1e-6, atol=1e-6)
