@@ -216,25 +216,39 @@ extern "C" int eqt_mix_tc_transposed(const float* g, const float* w_big, const f
 namespace eqt {
 namespace {
 
+// Launch of the weight-gradient kernel instance for `n_cols` output columns.
+int launch_wgrad(dim3 grid, size_t smem, cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mb, const WgradArgs& a) {
+  cudaError_t e = a.n_cols <= 64
+                      ? cudaFuncSetAttribute(wgrad_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)
+                      : cudaFuncSetAttribute(wgrad_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+  if (e != cudaSuccess) return fail(EQT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  if (a.n_cols <= 64)
+    wgrad_tc_kernel<64><<<grid, WgradCfg<64>::THREADS, smem, st>>>(ma, mb, a);
+  else
+    wgrad_tc_kernel<128><<<grid, WgradCfg<128>::THREADS, smem, st>>>(ma, mb, a);
+  return check_launch("wgrad_tc_kernel");
+}
+
 // Launch shape of the weight-gradient GEMM of one block: reduction rows per tile, M tiles, node splits and the
 // floats of scratch the per-CTA partial sums need.  Returns an error code for blocks that do not fit.
-struct WgradShape { int npt, m_tiles, splits, stages, chunk_tiles; size_t stage_bytes; int64_t K, need; };
+struct WgradShape { int npt, rows_pad, m_tiles, splits, stages, chunk_tiles; size_t stage_bytes; int64_t K, need; };
 int wgrad_shape(const eqt_mix_block& blk, int b, int64_t n, int cin, int cout, WgradShape* w) {
   if (blk.dim <= 0 || blk.dim > TILE_M || blk.paths <= 0) return fail(EQT_ERR_BAD_ARGUMENT, "bad block %d", b);
   const int b_boxes = cout / 32;
   const size_t budget = 220 * 1024 - 1024;
   w->K = (int64_t)blk.paths * cin;                               // M extent of this GEMM
   w->m_tiles = (int)ceil_div(w->K, 128);
-  // reduction rows per tile: multiple of 8 and of dim, two stages must fit in shared memory
+  // Reduction rows per tile: the most that leaves three stages in shared memory (with two, the TMA, split and MMA
+  // phases of the ring cannot overlap; smaller tiles pay more per-box issue cost per byte); whole nodes, padded with
+  // zero rows to a multiple of 8.
   const size_t bytes_per_row = 2 * (size_t)(4 + b_boxes) * 128;
-  const int rows_cap = (int)std::min<size_t>(128, budget / 2 / bytes_per_row);
-  int step = 8;
-  for (int d = blk.dim; d % 2 == 0 && step > 1; d /= 2) step /= 2;   // 8 / gcd(dim, 8)
-  w->npt = (rows_cap / blk.dim) / step * step;
-  if (w->npt <= 0) return fail(EQT_ERR_UNSUPPORTED, "irrep with %d components does not fit a reduction tile", blk.dim);
-  w->stage_bytes = bytes_per_row * (size_t)(w->npt * blk.dim);
-  w->stages = (int)std::min<size_t>(4, budget / w->stage_bytes);
-  w->chunk_tiles = std::max(1, 512 / (w->npt * blk.dim));
+  const int rows_target = std::max(8, (int)(budget / 3 / bytes_per_row) / 8 * 8);
+  w->npt = std::max(1, rows_target / blk.dim);
+  w->rows_pad = (w->npt * blk.dim + 7) / 8 * 8;
+  w->stage_bytes = bytes_per_row * (size_t)w->rows_pad;
+  w->stages = (int)std::min<size_t>(8, budget / w->stage_bytes);
+  if (w->stages < 2) return fail(EQT_ERR_UNSUPPORTED, "irrep with %d components does not fit a reduction tile", blk.dim);
+  w->chunk_tiles = std::max(1, 512 / w->rows_pad);
   const int64_t tiles = ceil_div(n, w->npt);
   w->splits = (int)std::max<int64_t>(1, std::min<int64_t>(tiles, sm_count() / w->m_tiles));
   w->need = (int64_t)w->splits * w->m_tiles * 128 * cout;
@@ -266,10 +280,6 @@ extern "C" int eqt_wgrad_tc(const float* s, const float* g, float* gw_packed, fl
   if (cin % 32 != 0 || cout % 32 != 0 || cout > 128)
     return fail(EQT_ERR_UNSUPPORTED, "tensor-core weight gradient needs C_in %% 32 == 0, C_out %% 32 == 0, C_out <= 128");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  {
-    cudaError_t e = cudaFuncSetAttribute(wgrad_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
-    if (e != cudaSuccess) return fail(EQT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-  }
   // every block is checked before the first launch, so a refusal leaves gw_packed untouched
   std::vector<WgradShape> shapes(num_blocks);
   for (int b = 0; b < num_blocks; ++b) {
@@ -285,10 +295,11 @@ extern "C" int eqt_wgrad_tc(const float* s, const float* g, float* gw_packed, fl
     const int m_tiles = w.m_tiles, npt = w.npt, splits = w.splits;
     const size_t stage_bytes = w.stage_bytes;
     WgradArgs a{};
-    a.n = n; a.dim = blk.dim; a.npt = npt; a.n_cols = cout; a.status = status;
+    a.n = n; a.dim = blk.dim; a.npt = npt; a.rows_pad = w.rows_pad; a.n_cols = cout; a.status = status;
     a.stages = w.stages;
+    a.issuers = w.rows_pad / 8 >= 2 ? 2 : 1;
     a.tmem_cols = 32;
-    while (a.tmem_cols < 2 * cout) a.tmem_cols <<= 1;
+    while (a.tmem_cols < 2 * a.issuers * cout) a.tmem_cols <<= 1;
     a.chunk_tiles = w.chunk_tiles;
     a.partial = scratch;
     CUtensorMap map_s, map_g;
@@ -307,8 +318,7 @@ extern "C" int eqt_wgrad_tc(const float* s, const float* g, float* gw_packed, fl
                             CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return rc;
     }
     dim3 grid((unsigned)splits, (unsigned)m_tiles);
-    wgrad_tc_kernel<<<grid, TC_THREADS, (size_t)a.stages * stage_bytes + 1024, st>>>(map_s, map_g, a);
-    if (int rc = check_launch("wgrad_tc_kernel")) return rc;
+    if (int rc = launch_wgrad(grid, (size_t)a.stages * stage_bytes + 1024, st, map_s, map_g, a)) return rc;
     wgrad_reduce_kernel<<<flat_grid(K * cout / 4, 256), 256, 0, st>>>(scratch, gw_packed + blk.w_offset, splits,
                                                                       (int64_t)m_tiles * 128, K, cout);
     if (int rc = check_launch("wgrad_reduce_kernel")) return rc;
@@ -398,13 +408,14 @@ extern "C" int eqt_outer_tc(const float* in1, const float* in2, float* out, floa
     const int b_boxes = c2 / 32;
     const size_t budget = 220 * 1024 - 1024;
     const size_t bytes_per_row = 2 * (size_t)(4 + b_boxes) * 128;
-    const int npt = (int)std::min<size_t>(128, budget / 2 / bytes_per_row) / 8 * 8;      // reduction rows per tile
+    const int npt = std::max(8, (int)(budget / 3 / bytes_per_row) / 8 * 8);          // reduction rows per tile
     WgradArgs a{};
-    a.n = n; a.dim = 1; a.npt = npt; a.n_cols = c2; a.status = status;
+    a.n = n; a.dim = 1; a.npt = npt; a.rows_pad = npt; a.n_cols = c2; a.status = status;
     const size_t stage_bytes = bytes_per_row * (size_t)npt;
-    a.stages = (int)std::min<size_t>(4, budget / stage_bytes);
+    a.stages = (int)std::min<size_t>(8, budget / stage_bytes);
+    a.issuers = npt / 8 >= 2 ? 2 : 1;
     a.tmem_cols = 32;
-    while (a.tmem_cols < 2 * c2) a.tmem_cols <<= 1;
+    while (a.tmem_cols < 2 * a.issuers * c2) a.tmem_cols <<= 1;
     a.chunk_tiles = std::max(1, 512 / npt);
     a.a_cols = a_cols; a.b_cols = b_cols;
     const int64_t tiles = ceil_div(n, npt);
@@ -425,11 +436,8 @@ extern "C" int eqt_outer_tc(const float* in1, const float* in2, float* out, floa
       cuuint32_t box[3] = {KB, 1, (cuuint32_t)npt};
       if (int rc = make_map(&map_b, in2, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return rc;
     }
-    cudaError_t e = cudaFuncSetAttribute(wgrad_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
-    if (e != cudaSuccess) return fail(EQT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     dim3 grid((unsigned)splits, (unsigned)m_tiles);
-    wgrad_tc_kernel<<<grid, TC_THREADS, (size_t)a.stages * stage_bytes + 1024, st>>>(map_a, map_b, a);
-    if (int rc = check_launch("wgrad_tc_kernel")) return rc;
+    if (int rc = launch_wgrad(grid, (size_t)a.stages * stage_bytes + 1024, st, map_a, map_b, a)) return rc;
   }
   // with no samples or no entries every unit list is read as empty only if m_tiles == 0; otherwise the partial sums
   // above were written by this call

@@ -142,6 +142,58 @@ __global__ void __launch_bounds__(256) ew_kernel_f4(P p) {
   }
 }
 
+// bfloat16 storage, C % 8 == 0, 16-byte aligned operands: eight channels per thread, 128-bit accesses, float sums,
+// 32-bit index arithmetic (the launcher checks that the element count fits).
+template <int OP>
+__global__ void __launch_bounds__(256) ew_kernel_b8(P p) {
+  const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(p.in1);
+  const __nv_bfloat16* y = static_cast<const __nv_bfloat16*>(p.in2);
+  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
+  const uint32_t C = (uint32_t)p.c1, C8 = C / 8, num_out = (uint32_t)p.num_out;
+  const uint32_t total = (uint32_t)p.n * num_out * C8;
+  for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+    const uint32_t c = (idx % C8) * 8;
+    const uint32_t o = (idx / C8) % num_out;
+    const int64_t n = idx / (C8 * num_out);
+    int64_t t0, t1;
+    seg_range(p, o, t0, t1);
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int64_t t = t0; t < t1; ++t) {
+      const Entry e = entry(p, t);
+      const uint4 xv = __ldg(reinterpret_cast<const uint4*>(x + n * p.bs1 + e.r1 * C + c));
+      const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+      float s = p.scale ? __ldg(static_cast<const float*>(p.scale) + e.tt) : 1.f;
+      float v[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(xp[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+      }
+      if (OP == EQT_OP_MUL) {
+        const uint4 yv = __ldg(reinterpret_cast<const uint4*>(y + n * p.bs2 + e.r2 * C + c));
+        const __nv_bfloat162* yp = reinterpret_cast<const __nv_bfloat162*>(&yv);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(yp[i]);
+          v[2 * i] *= f.x;
+          v[2 * i + 1] *= f.y;
+        }
+      }
+      if (OP == EQT_OP_VECSCA) s *= __bfloat162float(__ldg(y + n * p.bs2 + e.r2));
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += v[i] * s;
+    }
+    uint4 ov;
+    __nv_bfloat162* op2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) op2[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+    *reinterpret_cast<uint4*>(out + (n * p.out_size + out_row(p, o)) * C + c) = ov;
+  }
+}
+
 // Batch-summed form: out[o, c] = sum_n sum_t ...   block = 32 channels x 8 batch lanes,
 // grid = (num_out * channel tiles, batch chunks); one atomicAdd per block and output element.
 template <typename T, int OP>
@@ -442,6 +494,14 @@ int launch(const eqt_product_args& a, P p, cudaStream_t s) {
       if (op == EQT_OP_VECSCA) ew_kernel_f4<EQT_OP_VECSCA><<<grid, 256, 0, s>>>(p);
       if (op == EQT_OP_SCALE) ew_kernel_f4<EQT_OP_SCALE><<<grid, 256, 0, s>>>(p);
       return check_launch("ew_kernel_f4");
+    }
+    if (std::is_same<T, __nv_bfloat16>::value && p.c1 % 8 == 0 && aligned16(p.in1) && aligned16(p.out) &&
+        (op != EQT_OP_MUL || aligned16(p.in2)) && p.n * p.num_out * (p.c1 / 8) < (int64_t(1) << 31)) {
+      const unsigned grid = flat_grid(p.n * p.num_out * (p.c1 / 8), 256);
+      if (op == EQT_OP_MUL) ew_kernel_b8<EQT_OP_MUL><<<grid, 256, 0, s>>>(p);
+      if (op == EQT_OP_VECSCA) ew_kernel_b8<EQT_OP_VECSCA><<<grid, 256, 0, s>>>(p);
+      if (op == EQT_OP_SCALE) ew_kernel_b8<EQT_OP_SCALE><<<grid, 256, 0, s>>>(p);
+      return check_launch("ew_kernel_b8");
     }
     const unsigned grid = flat_grid(p.n * p.num_out * p.c1, 256);
     if (op == EQT_OP_MUL) ew_kernel<T, EQT_OP_MUL><<<grid, 256, 0, s>>>(p);
