@@ -2,7 +2,7 @@
 (l_max = 3, 64 channels, full 64 -> 64 channel mixing per path), on N GPUs of one box.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg5|cfg5q|cfg2|cfg1|cfg3|cfg4|featurize|epilogue]
-                    [--feature-mode uv|uu] [--repeats R] [--impl ours|reference|reference_triton] [--no-graph] [--no-cpu-baseline]
+                    [--feature-mode uv|uu] [--repeats R] [--impl ours|reference|reference_triton] [--no-graph] [--no-cpu-baseline] [--unfused-exchange]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
 One step = one pass of the layer over one synthetic graph: spherical harmonics of the edge vectors,
@@ -469,6 +469,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference_triton"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time the eager step only (no CUDA-graph replay)")
+    ap.add_argument("--unfused-exchange", action="store_true",
+                    help="N > 1: halo exchange and gradient all-reduce as separate operations around the layer "
+                         "(concatenated buffer, nothing overlapped) instead of the fused sharded layer")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -515,18 +518,25 @@ def main():
                                feature_mode=mode).to(dev)
     w_dev = weight.to(dev).requires_grad_(True)
     sh = enn.SphericalHarmonics(L_MAX)
-    x_dev = x_host.to(dev).requires_grad_(True)
+    # one GPU: the node features themselves; several: the rank's [owned | halo] buffer, halo rows filled by the layer
+    n_owned = plan.num_owned
+    x_dev = torch.zeros(plan.num_local if world > 1 else n_owned, *x_host.shape[1:], device=dev)
+    x_dev[:n_owned].copy_(x_host)
+    x_dev.requires_grad_(True)
     vec_dev = vec_host.to(dev).requires_grad_(True)
     loss_host = torch.empty(2, dtype=torch.float32).pin_memory()             # two slots: results are read one step late
     gw_host = torch.empty(2, *weight.shape).pin_memory()
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev) if args.workload == "cfg2" else None
 
     def step(x, vec):
-        local = halo_exchange(x, plan, send_index) if world > 1 else x
-        w = replicated(w_dev) if world > 1 else w_dev
-        out = layer(local, sh(vec), egraph, w)
+        if world > 1 and not args.unfused_exchange:
+            out = layer.forward_sharded(x, sh(vec), egraph, plan, send_index, w_dev)
+        elif world > 1:       # the exchange as separate differentiable operations around the single-GPU layer
+            out = layer(halo_exchange(x[:n_owned], plan, send_index), sh(vec), egraph, replicated(w_dev))
+        else:
+            out = layer(x, sh(vec), egraph, w_dev)
         gx, gv, gw = torch.autograd.grad(out, [x, vec, w_dev], cot)
-        return out, gx, gv, gw
+        return out, gx[:n_owned], gv, gw
 
     def barrier():
         torch.cuda.synchronize(dev)
@@ -616,7 +626,7 @@ def main():
     elapsed_ms = repeat_ms[len(repeat_ms) // 2] if len(repeat_ms) % 2 else 0.5 * (repeat_ms[len(repeat_ms) // 2 - 1] + repeat_ms[len(repeat_ms) // 2])
 
     # ---- checksum of one step (comparable across N: everything is summed over ranks) ----------------
-    out_c, gx_c, gv_c, gw_c = step(x_dev, vec_dev)
+    out_c, gx_c, gv_c, gw_c = (t.detach() for t in step(x_dev, vec_dev))
     sums = torch.stack([torch.dot(out_c.double().reshape(-1), cot.double().reshape(-1)), gx_c.double().sum(),
                         gx_c.double().square().sum(), gv_c.double().sum(), gv_c.double().square().sum()])
     if world > 1:
@@ -639,7 +649,7 @@ def main():
         with torch.cuda.stream(copy_stream), torch.no_grad():
             if i >= 2:
                 copy_stream.wait_event(consumed[slot])      # step i - 2 has finished with this buffer
-            bufs[slot][0].copy_(x_host, non_blocking=True)
+            bufs[slot][0][:n_owned].copy_(x_host, non_blocking=True)
             bufs[slot][1].copy_(vec_host, non_blocking=True)
             ready[slot].record(copy_stream)
 
@@ -677,6 +687,38 @@ def main():
     barrier()
     e2e_ms = e0_.elapsed_time(e1_)
     check_status()
+
+    # ---- N > 1: what the exchanges cost on their own (nothing to overlap with), and how large the halo is -----
+    exchange = None
+    if world > 1:
+        with torch.no_grad():
+            buf = x_dev.detach()
+            back = buf.new_empty((send_index.shape[0], *buf.shape[1:]))
+            gw_tmp = torch.zeros_like(w_dev)
+
+            def exchange_only():
+                dist.all_to_all_single(buf[n_owned:], buf[:n_owned].index_select(0, send_index), plan.recv_counts,
+                                       plan.send_counts)
+                dist.all_to_all_single(back, buf[n_owned:], plan.send_counts, plan.recv_counts)
+                dist.all_reduce(gw_tmp)
+
+            for _ in range(3):
+                exchange_only()
+            barrier()
+            x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            x0.record()
+            for _ in range(10):
+                exchange_only()
+            x1.record()
+            barrier()
+            stats = torch.tensor([x0.elapsed_time(x1) / 10, (plan.num_local - n_owned) / max(1, n_owned)],
+                                 dtype=torch.float64, device=dev)
+            dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        exchange = {"fused_with_layer": not args.unfused_exchange,
+                    "standalone_ms_per_step": round(float(stats[0]), 4),
+                    "standalone_is": "halo rows out + halo gradients back (all-to-all) + weight-gradient all-reduce, "
+                                     "back to back with no compute, maximum over ranks",
+                    "halo_rows_over_owned_rows_max": round(float(stats[1]), 4)}
 
     times = torch.tensor([e2e_ms, eager_ms], dtype=torch.float64, device=dev)
     if world > 1:
@@ -731,7 +773,7 @@ def main():
                                        if top in ncu_dram_bytes_cfg5q else None),
                     # whole step against the operator-boundary traffic of the per-edge layer (20,672 B per edge: x, y,
                     # out forward; g, x, y, gx, gy backward) - the figure the 70 % target is stated on
-                    "step_frac_opboundary": round(20672.0 * value / 1e9 / pk["hbm_gbs"], 4),
+                    "step_frac_opboundary": round(20672.0 * value / world / 1e9 / pk["hbm_gbs"], 4),
                     "step_opboundary_bytes_per_edge": 20672}
 
     result = {
@@ -743,7 +785,9 @@ def main():
         "checksum": checksum,
         "config": {"workload": label, "edges": n_edges_total, "nodes": graph.num_nodes, "irreps": IRREPS,
                    "channels": CHANNELS, "feature_mode": mode, "paths": PATHS,
-                   "parallelism": f"edges sharded by destination-node range over {world} GPU(s), halo rows by all-to-all",
+                   "parallelism": f"edges sharded by destination-node range over {world} GPU(s), halo rows by all-to-all"
+                                  + (" received in place, gradient exchanges asynchronous inside the backward pass"
+                                     if world > 1 and not args.unfused_exchange else ""),
                    "l2": ("working set >> 126 MB L2, no flush" if flush is None
                           else "256 MB written between steps to flush L2; steps timed individually")},
         "e2e": {"value": e2e_value, "unit": "edges/s", "ms_per_step": e2e_ms / steps,
@@ -757,6 +801,8 @@ def main():
         "cuda_graph": graphed is not None, "cuda_graph_error": graph_error,
         "eager_ms_per_step": round(eager_ms / steps, 4),
     }
+    if exchange is not None:
+        result["exchange"] = exchange
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             result["cpu_baseline"] = cpu_baseline(graph, x_all, cot_all, weight, mode)

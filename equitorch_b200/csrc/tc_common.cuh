@@ -156,6 +156,11 @@ inline int make_map(CUtensorMap* map, const float* base, int rank, const cuuint6
              const cuuint32_t* box, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn enc = encode_tiled();
   if (!enc) return fail(EQT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  // The encoder is a driver call and needs a current context; on a thread that has made no runtime call yet (an
+  // autograd worker whose first operation is this one) there is none until the runtime binds the primary context.
+  // cudaSetDevice does that and, unlike cudaFree(0), is legal while a stream is being captured.
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaSetDevice(dev);
   cuuint32_t ones[3] = {1, 1, 1};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<float*>(base), dims,
                    strides_bytes, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,

@@ -11,6 +11,13 @@ does cross ranks is the *input* of edges whose source lives elsewhere ("halo" no
 * backward: gradients of halo rows are sent back to their owners and added there; gradients of
   weights shared by all ranks are all-reduced.
 
+Two forms.  ``halo_exchange`` + ``replicated`` are differentiable building blocks around any per-rank layer.
+``sharded_layer`` runs the exchange and a layer given as separate passes (``forward``, ``grad_x``, ``grad_weight``,
+``grad_y``) as one operation on a preallocated ``[owned | halo]`` buffer: halo rows are received in place (no
+concatenation), the backward computes the gradient of the local rows first, sends the halo part back and all-reduces
+the weight gradient asynchronously while the remaining gradients are computed, and adds the returned rows with one
+``index_add_``.
+
 The reference has no multi-GPU mode; this module is the sharding the benchmark's scaling
 configuration asks for.  All planning happens once on the host from the global edge list.
 """
@@ -149,3 +156,74 @@ class _AllReduceGrad(torch.autograd.Function):
 
 def replicated(weight: Tensor, group=None) -> Tensor:
     return _AllReduceGrad.apply(weight, group)
+
+
+def _distributed(group=None) -> bool:
+    return dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+
+
+class _ShardedLayer(torch.autograd.Function):
+    """``local_x`` is the rank's ``(num_local, ...)`` buffer whose first ``num_owned`` rows are the owned rows; the
+    halo rows behind them are overwritten by the forward pass.  The returned gradient has the buffer's shape: owned
+    rows carry the full gradient (own edges + what other ranks returned), halo rows are zero."""
+
+    @staticmethod
+    def forward(ctx, local_x: Tensor, y: Tensor, weight: Tensor, ops, plan: ShardPlan, send_index: Tensor, group):
+        n_owned = plan.num_owned
+        if local_x.shape[0] != plan.num_local:
+            raise ValueError(f"local buffer has {local_x.shape[0]} rows, the plan needs {plan.num_local}")
+        buf = local_x.detach()
+        if _distributed(group):
+            dist.all_to_all_single(buf[n_owned:], buf[:n_owned].index_select(0, send_index), plan.recv_counts,
+                                   plan.send_counts, group=group)
+        elif buf.shape[0] > n_owned:       # single process holding a plan with halo rows: they are its own rows
+            buf[n_owned:] = buf[:n_owned].index_select(0, send_index)[: buf.shape[0] - n_owned]
+        out, state = ops.forward(buf, y, weight)
+        ctx.ops, ctx.plan, ctx.group, ctx.state = ops, plan, group, state
+        ctx.save_for_backward(send_index)
+        return out
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, grad: Tensor):
+        ops, plan, group, state = ctx.ops, ctx.plan, ctx.group, ctx.state
+        (send_index,) = ctx.saved_tensors
+        n_owned = plan.num_owned
+        grad = grad.contiguous()
+        multi = _distributed(group)
+        gx = gy = gw = back = work_x = work_w = None
+        if ctx.needs_input_grad[0]:
+            gx = ops.grad_x(state, grad)                       # (num_local, ...): own edges' contribution to every local row
+            if multi:
+                back = gx.new_empty((send_index.shape[0], *gx.shape[1:]))
+                work_x = dist.all_to_all_single(back, gx[n_owned:], plan.send_counts, plan.recv_counts, group=group,
+                                                async_op=True)
+        if ctx.needs_input_grad[2]:
+            gw = ops.grad_weight(state, grad).contiguous()
+            if multi:
+                work_w = dist.all_reduce(gw, group=group, async_op=True)
+        if ctx.needs_input_grad[1]:
+            gy = ops.grad_y(state, grad)
+        if gx is not None:
+            if work_x is not None:
+                work_x.wait()
+                gx[:n_owned].index_add_(0, send_index, back)
+            elif gx.shape[0] > n_owned:
+                gx[:n_owned].index_add_(0, send_index[: gx.shape[0] - n_owned], gx[n_owned:])
+            gx[n_owned:].zero_()
+        if work_w is not None:
+            work_w.wait()
+        return gx, gy, gw, None, None, None, None
+
+
+def sharded_layer(local_x: Tensor, y: Tensor, weight: Tensor, ops, plan: ShardPlan, send_index: Optional[Tensor] = None,
+                  group=None) -> Tensor:
+    """Halo exchange + layer + gradient exchange as one differentiable operation.
+
+    ``ops`` supplies the layer as four passes over the local rows: ``forward(local_x, y, weight) -> (out, state)``,
+    ``grad_x(state, grad) -> (num_local, ...)``, ``grad_weight(state, grad)`` and ``grad_y(state, grad)``
+    (``equitorch_b200.nn.functional.graph_tp.FusedGraphOps`` on a GPU).  ``local_x`` is modified in place (its halo
+    rows); the weight gradient comes back summed over ranks."""
+    if send_index is None:
+        send_index = plan.send_index.to(local_x.device)
+    return _ShardedLayer.apply(local_x, y, weight, ops, plan, send_index, group)

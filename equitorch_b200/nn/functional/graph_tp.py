@@ -69,16 +69,75 @@ def _mix(s: Tensor, w: Tensor, info, mode: str, tc: "MixPlan | None" = None) -> 
     return op(s, w, info.scale, info.index1, info.index2, info.seg_out, out_size=info.out_size)
 
 
-class SO3LinearGraphFunction(Function):
-    @staticmethod
-    def forward(ctx, node_x: Tensor, y: Tensor, weight: Tensor, graph: EdgeGraph, plan: GraphTPPlan, mode: str):
+class FusedGraphOps:
+    """The passes of the fused layer as separate calls, so that a caller can order them (the sharded layer sends halo
+    gradients back while the other gradients are computed).  ``state`` is what ``forward`` returns second."""
+
+    def __init__(self, graph: EdgeGraph, plan: GraphTPPlan, mode: str):
+        self.graph, self.plan, self.mode = graph, plan, mode
+
+    def forward(self, node_x: Tensor, y: Tensor, weight: Tensor):
+        graph, plan = self.graph, self.plan
         with _profile.timed("cg_segment_sum[fwd]"):
             s = cg_segment_sum(plan.fwd_table, node_x, y, graph.src_by_dst, graph.dst_order, graph.dst_ptr,
                                graph.num_dst)
         with _profile.timed("channel_mix[fwd]"):
-            out = _mix(s, weight, plan.mix_fwd, mode, plan.tc_fwd)
-        ctx.save_for_backward(node_x, y, weight, s if weight.requires_grad else None)
-        ctx.graph, ctx.plan, ctx.mode = graph, plan, mode
+            out = _mix(s, weight, plan.mix_fwd, self.mode, plan.tc_fwd)
+        return out, (node_x, y, weight, s if weight.requires_grad else None)
+
+    def _wt(self, weight: Tensor) -> Tensor:
+        return weight.transpose(-1, -2).contiguous() if self.mode == "uv" else weight
+
+    def grad_weight(self, state, grad: Tensor) -> Tensor:
+        _, _, weight, s = state
+        plan, mode, b2 = self.plan, self.mode, self.plan.mix_bwd2
+        with _profile.timed("weight_grad"):
+            tcw = plan.tc_fwd
+            if (mode == "uv" and tcw is not None and tcw.regular and grad.dtype == torch.float32
+                    and _tc_supported_w(weight.shape[-2], weight.shape[-1])):
+                return wgrad_tc(s, grad, tcw, weight.shape[0])
+            if mode == "uv":   # (P, Cout, Cin) summed over nodes, then transposed to the weight's layout
+                gw = _ops.indexed_outer_scale_gather(grad, s, b2.scale, b2.index1, b2.index2, b2.seg_out,
+                                                     out_accumulated=True, out_size=b2.out_size)
+                return gw.transpose(-1, -2).contiguous()
+            return _ops.indexed_mul_scale_gather(grad, s, b2.scale, b2.index1, b2.index2, b2.seg_out,
+                                                 out_accumulated=True, out_size=b2.out_size)
+
+    def grad_y(self, state, grad: Tensor) -> Tensor:
+        node_x, y, weight, _ = state
+        graph, plan, mode, b1 = self.graph, self.plan, self.mode, self.plan.mix_bwd1
+        # gradient w.r.t. the node-level intermediate: G[d, r] = g[d, M(r)] W[w(r)]^T
+        with _profile.timed("channel_mix[grad_inter]"):
+            tc = plan.tc_fwd
+            if (mode == "uv" and tc is not None and tc.regular
+                    and _tc_supported_t(weight.shape[-2], weight.shape[-1])):
+                g_inter = mix_tc_transposed(grad, weight, tc)
+            elif mode == "uv":
+                g_inter = _ops.indexed_vecmat_scale_gather(grad, self._wt(weight), b1.scale, b1.index2, b1.index1,
+                                                           b1.seg_out, out_size=b1.out_size)
+            else:
+                g_inter = _ops.indexed_mul_scale_gather(weight, grad, b1.scale, b1.index1, b1.index2, b1.seg_out,
+                                                        out_size=b1.out_size)
+        with _profile.timed("cg_inner[grad_y]"):
+            return cg_inner(plan.fwd_table, node_x, g_inter, graph.src_by_dst, graph.dst_ptr, graph.dst_sorted,
+                            graph.dst_order, y.shape[0])
+
+    def grad_x(self, state, grad: Tensor) -> Tensor:
+        _, y, weight, _ = state
+        graph, plan = self.graph, self.plan
+        with _profile.timed("cg_segment_sum[grad_x]"):
+            sx = cg_segment_sum(plan.bwd1_table, grad, y, graph.dst_by_src, graph.src_order, graph.src_ptr,
+                                graph.num_src)
+        with _profile.timed("channel_mix[grad_x]"):
+            return _mix(sx, self._wt(weight), plan.mix_src, self.mode, plan.tc_src)
+
+
+class SO3LinearGraphFunction(Function):
+    @staticmethod
+    def forward(ctx, node_x: Tensor, y: Tensor, weight: Tensor, graph: EdgeGraph, plan: GraphTPPlan, mode: str):
+        ctx.ops = FusedGraphOps(graph, plan, mode)
+        out, state = ctx.ops.forward(node_x, y, weight)
+        ctx.save_for_backward(*state)
         if _CHECK_EVERY_CALL:
             check_status(node_x.device)
         return out
@@ -86,47 +145,11 @@ class SO3LinearGraphFunction(Function):
     @staticmethod
     @torch.autograd.function.once_differentiable
     def backward(ctx, grad: Tensor):
-        node_x, y, weight, s = ctx.saved_tensors
-        graph, plan, mode = ctx.graph, ctx.plan, ctx.mode
+        state, ops = ctx.saved_tensors, ctx.ops
         grad = grad.contiguous()
-        gx = gy = gw = None
-        b1, b2 = plan.mix_bwd1, plan.mix_bwd2
-        wt = weight.transpose(-1, -2).contiguous() if mode == "uv" else weight
-        if ctx.needs_input_grad[2]:
-            with _profile.timed("weight_grad"):
-                tcw = plan.tc_fwd
-                if (mode == "uv" and tcw is not None and tcw.regular and grad.dtype == torch.float32
-                        and _tc_supported_w(weight.shape[-2], weight.shape[-1])):
-                    gw = wgrad_tc(s, grad, tcw, weight.shape[0])
-                elif mode == "uv":   # (P, Cout, Cin) summed over nodes, then transposed to the weight's layout
-                    gw = _ops.indexed_outer_scale_gather(grad, s, b2.scale, b2.index1, b2.index2, b2.seg_out,
-                                                         out_accumulated=True, out_size=b2.out_size)
-                    gw = gw.transpose(-1, -2).contiguous()
-                else:
-                    gw = _ops.indexed_mul_scale_gather(grad, s, b2.scale, b2.index1, b2.index2, b2.seg_out,
-                                                       out_accumulated=True, out_size=b2.out_size)
-        if ctx.needs_input_grad[1]:
-            # gradient w.r.t. the node-level intermediate: G[d, r] = g[d, M(r)] W[w(r)]^T
-            with _profile.timed("channel_mix[grad_inter]"):
-                tc = plan.tc_fwd
-                if (mode == "uv" and tc is not None and tc.regular
-                        and _tc_supported_t(weight.shape[-2], weight.shape[-1])):
-                    g_inter = mix_tc_transposed(grad, weight, tc)
-                elif mode == "uv":
-                    g_inter = _ops.indexed_vecmat_scale_gather(grad, wt, b1.scale, b1.index2, b1.index1, b1.seg_out,
-                                                               out_size=b1.out_size)
-                else:
-                    g_inter = _ops.indexed_mul_scale_gather(wt, grad, b1.scale, b1.index1, b1.index2, b1.seg_out,
-                                                            out_size=b1.out_size)
-            with _profile.timed("cg_inner[grad_y]"):
-                gy = cg_inner(plan.fwd_table, node_x, g_inter, graph.src_by_dst, graph.dst_ptr, graph.dst_sorted,
-                              graph.dst_order, y.shape[0])
-        if ctx.needs_input_grad[0]:
-            with _profile.timed("cg_segment_sum[grad_x]"):
-                sx = cg_segment_sum(plan.bwd1_table, grad, y, graph.dst_by_src, graph.src_order, graph.src_ptr,
-                                    graph.num_src)
-            with _profile.timed("channel_mix[grad_x]"):
-                gx = _mix(sx, wt, plan.mix_src, mode, plan.tc_src)
+        gw = ops.grad_weight(state, grad) if ctx.needs_input_grad[2] else None
+        gy = ops.grad_y(state, grad) if ctx.needs_input_grad[1] else None
+        gx = ops.grad_x(state, grad) if ctx.needs_input_grad[0] else None
         if _CHECK_EVERY_CALL:
             check_status(grad.device)
         return gx, gy, gw, None, None, None

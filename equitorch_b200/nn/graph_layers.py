@@ -8,7 +8,7 @@ import torch
 from torch import Tensor
 
 from ..graph import EdgeGraph
-from .functional.graph_tp import GraphTPPlan, so3_linear_graph
+from .functional.graph_tp import FusedGraphOps, GraphTPPlan, so3_linear_graph
 from .linears import SO3Linear
 
 
@@ -43,3 +43,16 @@ class SO3LinearGraph(SO3Linear):
         assert node_x.shape[0] == graph.num_src and edge_sh.shape[0] == graph.num_edges
         weight = self._resolve_weight(weight)
         return so3_linear_graph(node_x, edge_sh, weight, graph, self.plan(node_x.device), self.feature_mode)
+
+    def forward_sharded(self, local_x: Tensor, edge_sh: Tensor, graph: EdgeGraph, shard, send_index: Optional[Tensor] = None,
+                        weight: Optional[Tensor] = None, group=None) -> Tensor:
+        """One rank's part of the layer on a graph sharded by destination range (``equitorch_b200.dist``):
+        ``local_x`` is the rank's ``[owned | halo]`` buffer (halo rows are filled in place from their owners),
+        ``graph`` its local edges; returns the owned output rows.  Gradients: owned rows of ``local_x`` (including
+        what other ranks' edges contribute), ``edge_sh``, and the weight gradient summed over ranks."""
+        from ..dist import sharded_layer
+        weight = self._resolve_weight(weight)
+        if weight.ndim != (3 if self.feature_mode == "uv" else 2):
+            raise ValueError("the fused graph layer needs weights shared by all edges")
+        ops = FusedGraphOps(graph, self.plan(local_x.device), self.feature_mode)
+        return sharded_layer(local_x, edge_sh, weight, ops, shard, send_index, group)

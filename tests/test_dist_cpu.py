@@ -10,7 +10,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from equitorch_b200.dist import halo_exchange, partition_nodes_by_edges, plan_shards, replicated
+from equitorch_b200.dist import halo_exchange, partition_nodes_by_edges, plan_shards, replicated, sharded_layer
 from equitorch_b200.utils.synthetic import radius_graph, random_graph
 from oracle import tensor_products as otp
 
@@ -53,6 +53,69 @@ def _worker(rank, world, port, ret):
         ret[rank] = (plan.node_lo, plan.node_hi, plan.edge_lo, plan.edge_hi, out.detach(), gx, gv, gw)
     finally:
         dist.destroy_process_group()
+
+
+class _OracleOps:
+    """The layer as separate passes, computed by the CPU oracle (stands in for the CUDA passes of FusedGraphOps)."""
+
+    def __init__(self, plan):
+        self.plan = plan
+
+    def forward(self, local_x, y, weight):
+        with torch.enable_grad():
+            leaves = [t.detach().clone().requires_grad_(True) for t in (local_x, y, weight)]
+            out = otp.so3_linear_message_passing(leaves[0], leaves[1], self.plan.src_local, self.plan.dst_local, leaves[2],
+                                                 IR, IR, IR, feature_mode="uv", num_out_nodes=self.plan.num_owned)
+        return out.detach(), (leaves, out)
+
+    def _grad(self, state, grad, which):
+        leaves, out = state
+        return torch.autograd.grad(out, leaves[which], grad, retain_graph=True)[0]
+
+    def grad_x(self, state, grad):
+        return self._grad(state, grad, 0)
+
+    def grad_y(self, state, grad):
+        return self._grad(state, grad, 1)
+
+    def grad_weight(self, state, grad):
+        return self._grad(state, grad, 2)
+
+
+def _worker_fused(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g, x, w, cot = _inputs()
+        plan = plan_shards(g.src, g.dst, g.num_nodes, world)[rank]
+        local = torch.full((plan.num_local, *x.shape[1:]), float("nan"), dtype=x.dtype)     # halo rows start as garbage
+        local[:plan.num_owned] = x[plan.node_lo:plan.node_hi]
+        local.requires_grad_(True)
+        wr = w.clone().requires_grad_(True)
+        v = g.edge_vec[plan.edge_lo:plan.edge_hi].double().requires_grad_(True)
+        out = sharded_layer(local, v, wr, _OracleOps(plan), plan)
+        torch.testing.assert_close(local.detach()[plan.num_owned:], x[plan.halo_global])
+        gx, gv, gw = torch.autograd.grad(out, [local, v, wr], cot[plan.node_lo:plan.node_hi])
+        assert bool((gx[plan.num_owned:] == 0).all())
+        ret[rank] = (plan.node_lo, plan.node_hi, plan.edge_lo, plan.edge_hi, out.detach(), gx[:plan.num_owned], gv, gw)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sharded_layer_in_place_exchange_equals_single_process(world):
+    """`sharded_layer`: halo rows received into the preallocated buffer, halo gradients returned and the weight
+    gradient all-reduced asynchronously inside one backward pass."""
+    ref_out, ref_gx, ref_gv, ref_gw = _single()
+    ret = mp.Manager().dict()
+    mp.spawn(_worker_fused, args=(world, _free_port(), ret), nprocs=world, join=True)
+    assert sorted(ret.keys()) == list(range(world))
+    for rank in range(world):
+        lo, hi, e0, e1, out, gx, gv, gw = ret[rank]
+        torch.testing.assert_close(out, ref_out[lo:hi], rtol=1e-12, atol=1e-12)
+        torch.testing.assert_close(gx, ref_gx[lo:hi], rtol=1e-12, atol=1e-12)
+        torch.testing.assert_close(gv, ref_gv[e0:e1], rtol=1e-12, atol=1e-12)
+        torch.testing.assert_close(gw, ref_gw, rtol=1e-12, atol=1e-12)
 
 
 def _free_port():
