@@ -98,10 +98,12 @@ int launch_jobs(const GemmJob* jobs, int count, int64_t n, int* status, cudaStre
     for (int q = 0; q < m; ++q) L.max_cols = std::max(L.max_cols, jobs[first + q].N);
     const uint32_t a_bytes = TILE_M * KB * 4, b_bytes = (uint32_t)L.max_cols * KB * 4;
     uint32_t stage_bytes = 2 * a_bytes + 2 * b_bytes;
-    L.stages = (int)std::min<size_t>(8, (220 * 1024 - 1024) / stage_bytes);
+    const size_t epi_bytes = 4 * 32 * 36 * sizeof(float);      // the epilogue warps' transpose patches behind the ring
+    const size_t ring_budget = 220 * 1024 - 1024 - epi_bytes;
+    L.stages = (int)std::min<size_t>(8, ring_budget / stage_bytes);
     {   // A through tensor memory when at least four stages of 64 columns fit beside the two accumulators
       const uint32_t sb = a_bytes + 2 * b_bytes;
-      const int st = (int)std::min<size_t>(std::min<size_t>(8, (220 * 1024 - 1024) / sb), (512 - 2 * L.max_cols) / 64);
+      const int st = (int)std::min<size_t>(std::min<size_t>(8, ring_budget / sb), (512 - 2 * L.max_cols) / 64);
       if (st >= 4) {
         L.a_in_tmem = 1;
         L.stages = st;
@@ -142,7 +144,7 @@ int launch_jobs(const GemmJob* jobs, int count, int64_t n, int* status, cudaStre
     }
     L.total_tiles = total;
     const unsigned grid = (unsigned)std::min<int64_t>(total, sm_count());
-    mix_tc_kernel<<<grid, TC_THREADS + 32, (size_t)L.stages * stage_bytes + 1024, st>>>(L);
+    mix_tc_kernel<<<grid, TC_THREADS + 32, (size_t)L.stages * stage_bytes + 1024 + epi_bytes, st>>>(L);
     if (int rc = check_launch("mix_tc_kernel")) return rc;
   }
   return EQT_OK;
