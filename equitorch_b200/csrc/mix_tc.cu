@@ -98,7 +98,7 @@ int launch_jobs(const GemmJob* jobs, int count, int64_t n, int* status, cudaStre
     for (int q = 0; q < m; ++q) L.max_cols = std::max(L.max_cols, jobs[first + q].N);
     const uint32_t a_bytes = TILE_M * KB * 4, b_bytes = (uint32_t)L.max_cols * KB * 4;
     uint32_t stage_bytes = 2 * a_bytes + 2 * b_bytes;
-    const size_t epi_bytes = 4 * 32 * 36 * sizeof(float);      // the epilogue warps' transpose patches behind the ring
+    const size_t epi_bytes = EPI_PATCH_BYTES;                  // the epilogue warps' transpose patches behind the ring
     const size_t ring_budget = 220 * 1024 - 1024 - epi_bytes;
     L.stages = (int)std::min<size_t>(8, ring_budget / stage_bytes);
     {   // A through tensor memory when at least four stages of 64 columns fit beside the two accumulators
@@ -356,7 +356,7 @@ extern "C" int eqt_vecmat_tc(const float* x, const float* w, const int64_t* inde
   L.out = out; L.kb_begin = kb_begin; L.a_col = a_col; L.n = n; L.num_out = num_out; L.n_cols = cout; L.status = status;
   L.total_items = (int64_t)num_out * ceil_div(n, TILE_M);
   const uint32_t stage_bytes = TILE_M * KB * 4 + 2u * (uint32_t)cout * KB * 4;
-  L.stages = (int)std::min<size_t>(std::min<size_t>(8, (220 * 1024 - 1024) / stage_bytes), (512 - 2 * cout) / 64);
+  L.stages = (int)std::min<size_t>(std::min<size_t>(8, (220 * 1024 - 1024 - EPI_PATCH_BYTES) / stage_bytes), (512 - 2 * cout) / 64);
   if (L.stages < 2) return fail(EQT_ERR_UNSUPPORTED, "tile too wide for the shared-memory ring");
   L.tmem_cols = 32;
   while (L.tmem_cols < 2 * cout + 64 * L.stages) L.tmem_cols <<= 1;
@@ -377,7 +377,7 @@ extern "C" int eqt_vecmat_tc(const float* x, const float* w, const int64_t* inde
   cudaError_t e = cudaFuncSetAttribute(vecmat_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
   if (e != cudaSuccess) return fail(EQT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   const unsigned grid = (unsigned)std::min<int64_t>(L.total_items, sm_count());
-  vecmat_tc_kernel<<<grid, TC_THREADS, (size_t)L.stages * stage_bytes + 1024, st>>>(L);
+  vecmat_tc_kernel<<<grid, TC_THREADS, (size_t)L.stages * stage_bytes + 1024 + EPI_PATCH_BYTES, st>>>(L);
   return check_launch("vecmat_tc_kernel");
 }
 

@@ -115,6 +115,27 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// Epilogue store of a 32 x 32 accumulator block held one row per lane.  Written directly, every store instruction
+// would touch 32 rows with 16 bytes each; the block goes through the warp's shared-memory patch (32 rows, pitch
+// EPI_PITCH floats: 16-byte aligned rows, conflict-free in both directions) and leaves as eight instructions of four
+// full 128-byte row segments.  Lane l then serves columns 4 (l % 8) .. +3 of rows 4 i + l / 8, i = 0..7: `orow[i]`
+// points at that row's first served column (column offset included), bit i of `vmask` says whether the row exists.
+constexpr int EPI_PITCH = 36;
+constexpr int EPI_PATCH_BYTES = 4 * 32 * EPI_PITCH * 4;      // four epilogue warps
+__device__ __forceinline__ void store_block_rows(float* patch, const float (&v)[32], int lane, float* const (&orow)[8],
+                                                 unsigned vmask, int c0, int n_cols) {
+  __syncwarp();                                 // the previous block has been read out of the patch
+#pragma unroll
+  for (int c = 0; c < 32; c += 4)
+    *reinterpret_cast<float4*>(patch + lane * EPI_PITCH + c) = make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]);
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float4 t = *reinterpret_cast<const float4*>(patch + (i * 4 + (lane >> 3)) * EPI_PITCH + (lane & 7) * 4);
+    if (((vmask >> i) & 1) && c0 + (lane & 7) * 4 < n_cols) *reinterpret_cast<float4*>(orow[i] + c0) = t;
+  }
+}
+
 // lane i of the warp stores its 32 values to TMEM lane (base lane + i), columns [col, col + 32); the caller
 // issues tcgen05.wait::st before signalling anybody
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
