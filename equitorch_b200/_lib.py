@@ -98,10 +98,10 @@ SIGNATURES = {
                                        C.c_int32, C.c_void_p]),
     "eqt_wigner_d_backward": (C.c_int, [C.POINTER(WignerTableStruct), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                         C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p]),
-    "eqt_dense_rotation": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
-                                     C.c_void_p]),
-    "eqt_dense_rotation_grad_matrix": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32,
-                                                 C.c_void_p]),
+    "eqt_dense_rotation": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
+                                     C.c_int32, C.c_void_p]),
+    "eqt_dense_rotation_grad_matrix": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_void_p,
+                                                 C.c_int32, C.c_void_p]),
     "eqt_vecmat_tc": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
                                 C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p,
                                 C.c_void_p]),

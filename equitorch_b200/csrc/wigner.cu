@@ -192,11 +192,25 @@ __global__ void __launch_bounds__(256) wigner_d_backward_kernel(WigArgs a, int n
 // One CTA per sample: M (dim x dim) and x (dim x C) are staged in shared memory, M with the contraction index
 // outermost, so that a thread producing a 4 x 4 tile (4 rows, 4 channels) needs two 16-byte loads per contraction
 // step.  Rows and channels are padded to multiples of four inside shared memory only.
+// Asynchronous global -> shared copies of one element (4 or 8 bytes) or of 16 bytes.  Staging a sample through
+// registers (load, dependent store, next load) leaves one load in flight per thread: 30 elements per thread at the
+// latency of HBM each made these kernels latency bound at a fifth of the bandwidth; cp.async keeps them all in flight.
+template <int BYTES>
+__device__ __forceinline__ void cp_async(void* smem, const void* gmem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  if (BYTES == 16)
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+  else
+    asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(s), "l"(gmem), "n"(BYTES) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 template <typename T> struct alignas(16) Vec4 { T v[4]; };
 
 template <typename T>
 __global__ void __launch_bounds__(128) dense_rotation_kernel(const T* __restrict__ mat, const T* __restrict__ x, T* __restrict__ out,
-                                                             int64_t n, int dim, int c, int transposed) {
+                                                             int64_t n, int dim, int c, int transposed,
+                                                             const int32_t* __restrict__ row_range) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int dim4 = (dim + 3) & ~3, c4 = (c + 3) & ~3;
   T* ms = reinterpret_cast<T*>(smem_raw);        // [j][i padded to dim4]: ms[j * dim4 + i] = M[i][j] (or M[j][i] when transposed)
@@ -207,15 +221,20 @@ __global__ void __launch_bounds__(128) dense_rotation_kernel(const T* __restrict
   for (int64_t s = blockIdx.x; s < n; s += gridDim.x) {
     __syncthreads();
     const T* m = mat + s * dim * dim;
+    // row_range (block-diagonal matrices): only columns [lo, hi) of a row are read, the rest of `ms` keeps its zeros
     for (int r = threadIdx.x / 32; r < dim; r += blockDim.x / 32)
-      for (int q = threadIdx.x % 32; q < dim; q += 32) {          // element M[r][q]
-        const T v = __ldg(m + r * dim + q);
-        if (transposed) ms[r * dim4 + q] = v;                     // contraction index is the row
-        else ms[q * dim4 + r] = v;
-      }
+      for (int q = (row_range ? __ldg(row_range + 2 * r) : 0) + threadIdx.x % 32, qe = row_range ? __ldg(row_range + 2 * r + 1) : dim;
+           q < qe; q += 32)                                        // element M[r][q]; the contraction index is the row when transposed
+        cp_async<sizeof(T)>(transposed ? ms + r * dim4 + q : ms + q * dim4 + r, m + r * dim + q);
     const T* xin = x + s * dim * c;
-    for (int r = threadIdx.x / 32; r < dim; r += blockDim.x / 32)
-      for (int q = threadIdx.x % 32; q < c; q += 32) xs[r * c4 + q] = __ldg(xin + r * c + q);
+    if (c == c4 && (reinterpret_cast<uintptr_t>(xin) & 15u) == 0) {
+      constexpr int PER = 16 / sizeof(T);
+      for (int i = threadIdx.x; i < dim * c / PER; i += blockDim.x) cp_async<16>(xs + i * PER, xin + i * PER);
+    } else {
+      for (int r = threadIdx.x / 32; r < dim; r += blockDim.x / 32)
+        for (int q = threadIdx.x % 32; q < c; q += 32) cp_async<sizeof(T)>(xs + r * c4 + q, xin + r * c + q);
+    }
+    cp_async_wait_all();
     __syncthreads();
     T* o = out + s * dim * c;
     for (int i = threadIdx.x; i < rgroups * cgroups; i += blockDim.x) {
@@ -225,7 +244,13 @@ __global__ void __launch_bounds__(128) dense_rotation_kernel(const T* __restrict
       for (int u = 0; u < 4; ++u)
 #pragma unroll
         for (int w = 0; w < 4; ++w) acc[u][w] = T(0);
-      for (int j = 0; j < dim; ++j) {
+      int jlo = 0, jhi = dim;
+      if (row_range) {                             // contraction range of the tile's rows (the blocks are square)
+        const int r1 = min(r0 + 3, dim - 1);
+        jlo = __ldg(row_range + 2 * r0);
+        jhi = __ldg(row_range + 2 * r1 + 1);
+      }
+      for (int j = jlo; j < jhi; ++j) {
         const Vec4<T> xv = *reinterpret_cast<const Vec4<T>*>(xs + j * c4 + ch);
         const Vec4<T> mv = *reinterpret_cast<const Vec4<T>*>(ms + j * dim4 + r0);
 #pragma unroll
@@ -256,7 +281,8 @@ __global__ void __launch_bounds__(128) dense_rotation_kernel(const T* __restrict
 // 4 x 4 tile of grad_M from two 16-byte loads per channel
 template <typename T>
 __global__ void __launch_bounds__(256) dense_rotation_grad_matrix_kernel(const T* __restrict__ g, const T* __restrict__ x, T* __restrict__ gm,
-                                                                         int64_t n, int dim, int c) {
+                                                                         int64_t n, int dim, int c,
+                                                                         const int32_t* __restrict__ row_range) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int dim4 = (dim + 3) & ~3;
   T* gs = reinterpret_cast<T*>(smem_raw);        // [c][i padded to dim4]
@@ -269,9 +295,10 @@ __global__ void __launch_bounds__(256) dense_rotation_grad_matrix_kernel(const T
     // row pitch dim4 (odd multiples of four words spread over the banks well enough for this one pass)
     for (int r = threadIdx.x / 32; r < dim; r += blockDim.x / 32)
       for (int k = threadIdx.x % 32; k < c; k += 32) {
-        gs[k * dim4 + r] = __ldg(g + (s * dim + r) * c + k);
-        xs[k * dim4 + r] = __ldg(x + (s * dim + r) * c + k);
+        cp_async<sizeof(T)>(gs + k * dim4 + r, g + (s * dim + r) * c + k);
+        cp_async<sizeof(T)>(xs + k * dim4 + r, x + (s * dim + r) * c + k);
       }
+    cp_async_wait_all();
     __syncthreads();
     T* o = gm + s * dim * dim;
     for (int i = threadIdx.x; i < groups * groups; i += blockDim.x) {
@@ -281,7 +308,13 @@ __global__ void __launch_bounds__(256) dense_rotation_grad_matrix_kernel(const T
       for (int u = 0; u < 4; ++u)
 #pragma unroll
         for (int w = 0; w < 4; ++w) acc[u][w] = T(0);
-      for (int k = 0; k < c; ++k) {
+      // block-diagonal matrices: a tile outside every block of its rows is written as zeros without the products
+      bool inside = true;
+      if (row_range) {
+        const int p1 = min(p0 + 3, dim - 1);
+        inside = p0 < dim && q0 < __ldg(row_range + 2 * p1 + 1) && q0 + 4 > __ldg(row_range + 2 * p0);
+      }
+      for (int k = 0; k < (inside ? c : 0); ++k) {
         const Vec4<T> gv = *reinterpret_cast<const Vec4<T>*>(gs + k * dim4 + p0);
         const Vec4<T> xv = *reinterpret_cast<const Vec4<T>*>(xs + k * dim4 + q0);
 #pragma unroll
@@ -293,7 +326,11 @@ __global__ void __launch_bounds__(256) dense_rotation_grad_matrix_kernel(const T
       for (int u = 0; u < 4; ++u)
 #pragma unroll
         for (int w = 0; w < 4; ++w)
-          if (p0 + u < dim && q0 + w < dim) o[(p0 + u) * dim + q0 + w] = acc[u][w];
+          if (p0 + u < dim && q0 + w < dim) {
+            // inside a straddling tile, entries outside the row's own block are zero as well
+            const bool keep = !row_range || (q0 + w >= __ldg(row_range + 2 * (p0 + u)) && q0 + w < __ldg(row_range + 2 * (p0 + u) + 1));
+            o[(p0 + u) * dim + q0 + w] = keep ? acc[u][w] : T(0);
+          }
     }
   }
 }
@@ -360,7 +397,7 @@ extern "C" int eqt_wigner_d_backward(const eqt_wigner_table* table, const void* 
 }
 
 extern "C" int eqt_dense_rotation(const void* matrix, const void* x, void* out, int64_t n, int32_t dim, int32_t channels,
-                                  int32_t transposed, int32_t dtype, void* stream) {
+                                  int32_t transposed, const int32_t* row_range, int32_t dtype, void* stream) {
   using namespace eqt;
   if (n < 0 || dim <= 0 || channels <= 0) return fail(EQT_ERR_BAD_ARGUMENT, "bad sizes");
   if (dtype != EQT_F32 && dtype != EQT_F64) return fail(EQT_ERR_UNSUPPORTED, "float32 or float64 only");
@@ -370,21 +407,27 @@ extern "C" int eqt_dense_rotation(const void* matrix, const void* x, void* out, 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const size_t bytes = es * ((size_t)dim * ((dim + 3) & ~3) + (size_t)dim * ((channels + 3) & ~3));
   if (bytes > 200 * 1024) return fail(EQT_ERR_UNSUPPORTED, "matrix and features of one sample do not fit shared memory");
-  const unsigned grid = flat_grid(n, 1, 16);
+  // one resident wave: samples are strided over the CTAs, and a second, partial wave would run at a fraction of the occupancy
+  auto wave = [&](auto kernel, int threads) {
+    int per_sm = 1;
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, bytes) != cudaSuccess || per_sm < 1) per_sm = 1;
+    return (unsigned)std::min<int64_t>(n, (int64_t)sm_count() * per_sm);
+  };
   if (dtype == EQT_F32) {
-    cudaFuncSetAttribute(dense_rotation_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    const unsigned grid = wave(dense_rotation_kernel<float>, 128);
     dense_rotation_kernel<float><<<grid, 128, bytes, st>>>(static_cast<const float*>(matrix), static_cast<const float*>(x),
-                                                            static_cast<float*>(out), n, dim, channels, transposed);
+                                                            static_cast<float*>(out), n, dim, channels, transposed, row_range);
   } else {
-    cudaFuncSetAttribute(dense_rotation_kernel<double>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    const unsigned grid = wave(dense_rotation_kernel<double>, 128);
     dense_rotation_kernel<double><<<grid, 128, bytes, st>>>(static_cast<const double*>(matrix), static_cast<const double*>(x),
-                                                             static_cast<double*>(out), n, dim, channels, transposed);
+                                                             static_cast<double*>(out), n, dim, channels, transposed, row_range);
   }
   return check_launch("dense_rotation_kernel");
 }
 
 extern "C" int eqt_dense_rotation_grad_matrix(const void* grad_out, const void* x, void* grad_matrix, int64_t n, int32_t dim,
-                                              int32_t channels, int32_t dtype, void* stream) {
+                                              int32_t channels, const int32_t* row_range, int32_t dtype, void* stream) {
   using namespace eqt;
   if (n < 0 || dim <= 0 || channels <= 0) return fail(EQT_ERR_BAD_ARGUMENT, "bad sizes");
   if (dtype != EQT_F32 && dtype != EQT_F64) return fail(EQT_ERR_UNSUPPORTED, "float32 or float64 only");
@@ -394,15 +437,20 @@ extern "C" int eqt_dense_rotation_grad_matrix(const void* grad_out, const void* 
   const size_t bytes = es * 2 * (size_t)channels * ((dim + 3) & ~3);
   if (bytes > 200 * 1024) return fail(EQT_ERR_UNSUPPORTED, "features of one sample do not fit shared memory");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const unsigned grid = flat_grid(n, 1, 16);
+  auto wave = [&](auto kernel, int threads) {
+    int per_sm = 1;
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, bytes) != cudaSuccess || per_sm < 1) per_sm = 1;
+    return (unsigned)std::min<int64_t>(n, (int64_t)sm_count() * per_sm);
+  };
   if (dtype == EQT_F32) {
-    cudaFuncSetAttribute(dense_rotation_grad_matrix_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    const unsigned grid = wave(dense_rotation_grad_matrix_kernel<float>, 256);
     dense_rotation_grad_matrix_kernel<float><<<grid, 256, bytes, st>>>(static_cast<const float*>(grad_out), static_cast<const float*>(x),
-                                                                        static_cast<float*>(grad_matrix), n, dim, channels);
+                                                                        static_cast<float*>(grad_matrix), n, dim, channels, row_range);
   } else {
-    cudaFuncSetAttribute(dense_rotation_grad_matrix_kernel<double>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    const unsigned grid = wave(dense_rotation_grad_matrix_kernel<double>, 256);
     dense_rotation_grad_matrix_kernel<double><<<grid, 256, bytes, st>>>(static_cast<const double*>(grad_out), static_cast<const double*>(x),
-                                                                         static_cast<double*>(grad_matrix), n, dim, channels);
+                                                                         static_cast<double*>(grad_matrix), n, dim, channels, row_range);
   }
   return check_launch("dense_rotation_grad_matrix_kernel");
 }

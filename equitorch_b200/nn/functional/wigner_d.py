@@ -34,13 +34,14 @@ def sparse_wigner_rotation(input: Tensor, sincos_alpha: Optional[Tensor], sincos
 
 
 class _DenseRotation(torch.autograd.Function):
-    """``matrix (N, D, D) @ x (N, D, C)`` (``transposed``: ``matrix^T @ x``) on the shared-memory kernels."""
+    """``matrix (N, D, D) @ x (N, D, C)`` (``transposed``: ``matrix^T @ x``) on the shared-memory kernels.
+    ``row_range``: the matrices are block diagonal (see ``ops.wigner_op.block_row_range``)."""
 
     @staticmethod
-    def forward(ctx, x: Tensor, matrix: Tensor, transposed: bool):
+    def forward(ctx, x: Tensor, matrix: Tensor, transposed: bool, row_range):
         ctx.save_for_backward(x if matrix.requires_grad else None, matrix if x.requires_grad else None)
-        ctx.transposed = transposed
-        return _wop.dense_rotation(matrix, x, transposed)
+        ctx.transposed, ctx.row_range = transposed, row_range
+        return _wop.dense_rotation(matrix, x, transposed, row_range)
 
     @staticmethod
     def backward(ctx, grad: Tensor):
@@ -48,39 +49,43 @@ class _DenseRotation(torch.autograd.Function):
         grad = grad.contiguous()
         gx = gm = None
         if ctx.needs_input_grad[0]:
-            gx = _DenseRotation.apply(grad, matrix, not ctx.transposed)
+            gx = _DenseRotation.apply(grad, matrix, not ctx.transposed, ctx.row_range)
         if ctx.needs_input_grad[1]:
             # d/dM of M x is g x^T; of M^T x it is x g^T
-            gm = _RotationGradMatrix.apply(x, grad) if ctx.transposed else _RotationGradMatrix.apply(grad, x)
-        return gx, gm, None
+            gm = (_RotationGradMatrix.apply(x, grad, ctx.row_range) if ctx.transposed
+                  else _RotationGradMatrix.apply(grad, x, ctx.row_range))
+        return gx, gm, None, None
 
 
 class _RotationGradMatrix(torch.autograd.Function):
-    """``a (N, D, C), b (N, D, C) -> a @ b^T (N, D, D)``."""
+    """``a (N, D, C), b (N, D, C) -> a @ b^T (N, D, D)`` (restricted to the diagonal blocks with ``row_range``)."""
 
     @staticmethod
-    def forward(ctx, a: Tensor, b: Tensor):
+    def forward(ctx, a: Tensor, b: Tensor, row_range):
         ctx.save_for_backward(a if b.requires_grad else None, b if a.requires_grad else None)
-        return _wop.dense_rotation_grad_matrix(a.contiguous(), b.contiguous())
+        ctx.row_range = row_range
+        return _wop.dense_rotation_grad_matrix(a.contiguous(), b.contiguous(), row_range)
 
     @staticmethod
     def backward(ctx, grad: Tensor):
         a, b = ctx.saved_tensors
         grad = grad.contiguous()
-        ga = _DenseRotation.apply(b, grad, False) if ctx.needs_input_grad[0] else None      # g b
-        gb = _DenseRotation.apply(a, grad, True) if ctx.needs_input_grad[1] else None       # g^T a
-        return ga, gb
+        ga = _DenseRotation.apply(b, grad, False, ctx.row_range) if ctx.needs_input_grad[0] else None      # g b
+        gb = _DenseRotation.apply(a, grad, True, ctx.row_range) if ctx.needs_input_grad[1] else None       # g^T a
+        return ga, gb, None
 
 
-def dense_wigner_rotation(input: Tensor, wigner_d: Tensor) -> Tensor:
+def dense_wigner_rotation(input: Tensor, wigner_d: Tensor, row_range: Optional[Tensor] = None) -> Tensor:
     """``wigner_d (N, dim, dim) @ input (N, dim, C)``.  A ``wigner_d`` that is the transposed view of a contiguous
-    tensor (``d.transpose(-1, -2)``, the inverse rotation) is applied without materialising the transpose."""
+    tensor (``d.transpose(-1, -2)``, the inverse rotation) is applied without materialising the transpose.
+    ``row_range`` declares the matrices block diagonal over the irreps: only the blocks are read and multiplied, and
+    the gradient with respect to ``wigner_d`` is zero outside them."""
     if wigner_d.ndim == 3 and input.ndim == 3:
         if wigner_d.is_contiguous() and _wop.rotation_supported(wigner_d, input):
-            return _DenseRotation.apply(input.contiguous(), wigner_d, False)
+            return _DenseRotation.apply(input.contiguous(), wigner_d, False, row_range)
         base = wigner_d.transpose(-1, -2)
         if base.is_contiguous() and _wop.rotation_supported(base, input):
-            return _DenseRotation.apply(input.contiguous(), base, True)
+            return _DenseRotation.apply(input.contiguous(), base, True, row_range)
     return wigner_d @ input
 
 

@@ -35,17 +35,26 @@ class SparseWignerRotation(_WithRotationInfo):
 
 
 class DenseWignerRotation(nn.Module):
-    """``wigner_d (N, dim, dim) @ input (N, dim, C)``."""
+    """``wigner_d (N, dim, dim) @ input (N, dim, C)``.
 
-    def __init__(self, irreps: Irreps):
+    A Wigner D-matrix is block diagonal over the irreps (455 of 2401 entries for l = 0..6).  With ``block_diagonal``
+    (the default) the CUDA kernels read and multiply only those blocks and return a ``wigner_d`` gradient that is zero
+    outside them; pass ``block_diagonal=False`` to multiply by arbitrary dense matrices."""
+
+    def __init__(self, irreps: Irreps, block_diagonal: bool = True):
         super().__init__()
         self.irreps = check_irreps(irreps)
+        self.block_diagonal = block_diagonal
 
     def forward(self, input: Tensor, wigner_d: Tensor) -> Tensor:
-        return dense_wigner_rotation(input, wigner_d)
+        row_range = None
+        if self.block_diagonal and input.is_cuda and wigner_d.shape[-1] == self.irreps.dim:
+            from ..ops.wigner_op import block_row_range
+            row_range = block_row_range(self.irreps, input.device)
+        return dense_wigner_rotation(input, wigner_d, row_range)
 
     def extra_repr(self) -> str:
-        return f"irreps={self.irreps}"
+        return f"irreps={self.irreps}, block_diagonal={self.block_diagonal}"
 
 
 class WignerD(_WithRotationInfo):

@@ -98,25 +98,44 @@ def wigner_d_backward(table: WignerTable, alpha: Tensor, beta: Tensor, gamma: Te
     return grads[0], grads[1], grads[2]
 
 
-def dense_rotation(matrix: Tensor, x: Tensor, transposed: bool = False) -> Tensor:
-    """``out[n] = matrix[n] @ x[n]`` (or ``matrix[n].T @ x[n]``); matrix (N, D, D), x (N, D, C), contiguous."""
+_row_ranges: Dict[Tuple, Tensor] = {}
+
+
+def block_row_range(irreps: Irreps, device) -> Tensor:
+    """(dim, 2) int32: for every row of a matrix that is block diagonal over ``irreps`` the column range of its block."""
+    key = (tuple(ir.dim for ir in irreps), torch.device(device))
+    if key not in _row_ranges:
+        rows, start = [], 0
+        for ir in irreps:
+            rows += [(start, start + ir.dim)] * ir.dim
+            start += ir.dim
+        _row_ranges[key] = torch.tensor(rows, dtype=torch.int32, device=device).contiguous()
+    return _row_ranges[key]
+
+
+def dense_rotation(matrix: Tensor, x: Tensor, transposed: bool = False, row_range: Tensor = None) -> Tensor:
+    """``out[n] = matrix[n] @ x[n]`` (or ``matrix[n].T @ x[n]``); matrix (N, D, D), x (N, D, C), contiguous.
+    ``row_range`` (see :func:`block_row_range`): the matrices are block diagonal, entries outside the blocks are
+    neither read nor multiplied."""
     dev = _lib.require_cuda(matrix, x)
     n, d, c = x.shape
     out = torch.empty_like(x)
     with torch.cuda.device(dev):
         _lib.check(_lib.lib().eqt_dense_rotation(matrix.data_ptr(), x.data_ptr(), out.data_ptr(), n, d, c, int(transposed),
-                                                 _lib.DTYPE_CODE[x.dtype], _lib.stream_ptr(dev)), "eqt_dense_rotation")
+                                                 _lib.ptr(row_range), _lib.DTYPE_CODE[x.dtype], _lib.stream_ptr(dev)),
+                   "eqt_dense_rotation")
     return out
 
 
-def dense_rotation_grad_matrix(grad_out: Tensor, x: Tensor) -> Tensor:
-    """``grad_matrix[n] = grad_out[n] @ x[n].T``."""
+def dense_rotation_grad_matrix(grad_out: Tensor, x: Tensor, row_range: Tensor = None) -> Tensor:
+    """``grad_matrix[n] = grad_out[n] @ x[n].T`` (with ``row_range``: zero outside the diagonal blocks)."""
     dev = _lib.require_cuda(grad_out, x)
     n, d, c = x.shape
     gm = torch.empty(n, d, d, dtype=x.dtype, device=dev)
     with torch.cuda.device(dev):
         _lib.check(_lib.lib().eqt_dense_rotation_grad_matrix(grad_out.data_ptr(), x.data_ptr(), gm.data_ptr(), n, d, c,
-                                                             _lib.DTYPE_CODE[x.dtype], _lib.stream_ptr(dev)),
+                                                             _lib.ptr(row_range), _lib.DTYPE_CODE[x.dtype],
+                                                             _lib.stream_ptr(dev)),
                    "eqt_dense_rotation_grad_matrix")
     return gm
 

@@ -381,11 +381,14 @@ int eqt_wigner_d_backward(const eqt_wigner_table* table, const void* alpha, cons
  * to the matrix, grad_matrix[n, i, j] = sum_c grad_out[n, i, c] x[n, j, c].  float32 / float64.
  * replaces: dense_wigner_rotation = `wigner_d @ input` (equitorch/nn/functional/wigner_d.py:58-72,
  *   equitorch/nn/wigner_d.py:89-106) and the two batched products of its backward pass.
+ * row_range (optional, device, dim x 2 int32): for matrices that are block diagonal over irreps, the column range
+ *   [lo, hi) of every row's block.  Only those entries of `matrix` are read and multiplied, and grad_matrix is zero
+ *   outside them.  NULL = dense.
  */
 int eqt_dense_rotation(const void* matrix, const void* x, void* out, int64_t n, int32_t dim, int32_t channels,
-                       int32_t transposed, int32_t dtype, void* stream);
+                       int32_t transposed, const int32_t* row_range, int32_t dtype, void* stream);
 int eqt_dense_rotation_grad_matrix(const void* grad_out, const void* x, void* grad_matrix, int64_t n, int32_t dim,
-                                   int32_t channels, int32_t dtype, void* stream);
+                                   int32_t channels, const int32_t* row_range, int32_t dtype, void* stream);
 
 /*
  * Radius graph and edge features in one pass over a cell list (float32).

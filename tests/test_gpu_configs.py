@@ -120,22 +120,34 @@ def test_config4_wigner_d_generation():
     assert _rel(d_s, d_g[:512]) < 1e-5
 
 
-def test_config4_dense_rotation():
+@pytest.mark.parametrize("block_diagonal", [False, True])
+def test_config4_dense_rotation(block_diagonal):
     """D x, D^T x and their gradients with respect to x and D at 20k samples (49 x 49 matrices, 32 channels), own
-    kernels against float64 matmul, bound 1e-5."""
+    kernels against float64 matmul, bound 1e-5.  Dense matrices with ``block_diagonal=False``; matrices that are block
+    diagonal over l = 0..6 with the default, where only the blocks are read and the matrix gradient is the float64
+    gradient restricted to the blocks."""
     e, c = 20_000, 32
     g, x, _, cot = _config4_inputs(e, c)
     d = torch.randn(e, 49, 49, generator=g) / 7
-    rot = enn.DenseWignerRotation(Irreps((0, 6)))
+    mask = torch.zeros(49, 49)
+    for l in range(7):
+        mask[l * l:(l + 1) ** 2, l * l:(l + 1) ** 2] = 1
+    if block_diagonal:
+        d = d * mask
+    rot = enn.DenseWignerRotation(Irreps((0, 6)), block_diagonal=block_diagonal)
     for transposed in (False, True):
         xo, do = x.double().requires_grad_(True), d.double().requires_grad_(True)
         ref = (do.transpose(-1, -2) if transposed else do) @ xo
-        gro = torch.autograd.grad(ref, [xo, do], cot.double())
+        gro = list(torch.autograd.grad(ref, [xo, do], cot.double()))
+        if block_diagonal:
+            gro[1] = gro[1] * mask.double()
         xg, dg = x.to(DEV).requires_grad_(True), d.to(DEV).requires_grad_(True)
         out = rot(xg, dg.transpose(-1, -2) if transposed else dg)
         grg = torch.autograd.grad(out, [xg, dg], cot.to(DEV))
         for u, v in [(out, ref), *zip(grg, gro)]:
             assert _rel(u, v) < 1e-5
+        if block_diagonal:
+            assert bool((grg[1].cpu() * (1 - mask) == 0).all())
 
 
 def test_config4_so2_linear():
