@@ -42,6 +42,7 @@ struct WigArgs {
   void* gc;
   int64_t n;
   int dim, max_l, coef_count;
+  int block_elems;              // capacity of the forward kernel's in-block element list (dim * dim always suffices)
 };
 
 template <typename T> __device__ __forceinline__ void sincos_t(T x, T* s, T* c);
@@ -109,16 +110,27 @@ __global__ void __launch_bounds__(256) wigner_d_forward_kernel(WigArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   T* coef = reinterpret_cast<T*>(smem_raw);
   T* tr = coef + a.coef_count;                                  // [WIG_EPB][3][L1][2]
-  // per element of the dim x dim matrix: -1 outside the blocks, else (coefficient offset << 12) | (l << 8) | ((p + l) << 4) | (q + l)
-  int32_t* elem = reinterpret_cast<int32_t*>(tr + WIG_EPB * 3 * (a.max_l + 1) * 2);
+  // in-block elements of the dim x dim matrix: position and (coefficient offset << 12) | (l << 8) | ((p + l) << 4) | (q + l);
+  // `img` holds one sample's matrix: zeros outside the blocks (written once), the blocks rewritten per sample, so that
+  // only block elements cost arithmetic and every sample leaves as one linear, coalesced copy
+  int32_t* elem = reinterpret_cast<int32_t*>(tr + WIG_EPB * 3 * (a.max_l + 1) * 2);     // [count][2]
   const int L1 = a.max_l + 1, dim = a.dim, dd = dim * dim;
+  T* img = reinterpret_cast<T*>(elem + 2 * a.block_elems);
+  __shared__ int count_s;
+  if (threadIdx.x == 0) count_s = 0;
   for (int i = threadIdx.x; i < a.coef_count; i += blockDim.x) coef[i] = static_cast<const T*>(a.coef)[i];
+  for (int i = threadIdx.x; i < dd; i += blockDim.x) img[i] = T(0);
+  __syncthreads();
   for (int i = threadIdx.x; i < dd; i += blockDim.x) {
     const int P = i / dim, Q = i % dim;
     const int32_t* cp = a.comp + 4 * P;
     const int32_t* cq = a.comp + 4 * Q;
-    const int l = __ldg(cp + 1);
-    elem[i] = __ldg(cp) == __ldg(cq) ? (__ldg(cp + 2) << 12) | (l << 8) | ((__ldg(cp + 3) + l) << 4) | (__ldg(cq + 3) + l) : -1;
+    if (__ldg(cp) == __ldg(cq)) {
+      const int l = __ldg(cp + 1);
+      const int slot = atomicAdd(&count_s, 1);      // any order: every element is written by exactly one thread per sample
+      elem[2 * slot] = i;
+      elem[2 * slot + 1] = (__ldg(cp + 2) << 12) | (l << 8) | ((__ldg(cp + 3) + l) << 4) | (__ldg(cq + 3) + l);
+    }
   }
   const T* angles[3] = {static_cast<const T*>(a.alpha), static_cast<const T*>(a.beta), static_cast<const T*>(a.gamma)};
   T* out = static_cast<T*>(a.d);
@@ -130,18 +142,19 @@ __global__ void __launch_bounds__(256) wigner_d_forward_kernel(WigArgs a) {
       fill_trig<T>(tr + s * 3 * L1 * 2, L1, which, k, angles[which][s0 + s]);
     }
     __syncthreads();
+    const int count = count_s;
     for (int s = 0; s < ns; ++s) {
-      T* o = out + (s0 + s) * dd;
-      for (int r = threadIdx.x; r < dd; r += blockDim.x) {
-        const int32_t code = elem[r];
-        T v = T(0);
-        if (code >= 0) {                                        // inside an irrep block
-          const int l = (code >> 8) & 15;
-          T u0, u1, u2;
-          wigner_element<T, false>(coef + (code >> 12), tr + s * 3 * L1 * 2, L1, l, ((code >> 4) & 15) - l, (code & 15) - l, v, u0, u1, u2);
-        }
-        o[r] = v;
+      for (int e = threadIdx.x; e < count; e += blockDim.x) {
+        const int32_t code = elem[2 * e + 1];
+        const int l = (code >> 8) & 15;
+        T v, u0, u1, u2;
+        wigner_element<T, false>(coef + (code >> 12), tr + s * 3 * L1 * 2, L1, l, ((code >> 4) & 15) - l, (code & 15) - l, v, u0, u1, u2);
+        img[elem[2 * e]] = v;
       }
+      __syncthreads();
+      T* o = out + (s0 + s) * dd;
+      for (int r = threadIdx.x; r < dd; r += blockDim.x) o[r] = img[r];
+      __syncthreads();
     }
   }
 }
@@ -287,6 +300,7 @@ __global__ void __launch_bounds__(256) dense_rotation_grad_matrix_kernel(const T
   const int dim4 = (dim + 3) & ~3;
   T* gs = reinterpret_cast<T*>(smem_raw);        // [c][i padded to dim4]
   T* xs = gs + c * dim4;
+  T* img = xs + c * dim4;                        // [dim][dim] result of the current sample
   for (int i = threadIdx.x; i < 2 * c * dim4; i += blockDim.x) gs[i] = T(0);
   const int groups = dim4 / 4;
   for (int64_t s = blockIdx.x; s < n; s += gridDim.x) {
@@ -329,9 +343,13 @@ __global__ void __launch_bounds__(256) dense_rotation_grad_matrix_kernel(const T
           if (p0 + u < dim && q0 + w < dim) {
             // inside a straddling tile, entries outside the row's own block are zero as well
             const bool keep = !row_range || (q0 + w >= __ldg(row_range + 2 * (p0 + u)) && q0 + w < __ldg(row_range + 2 * (p0 + u) + 1));
-            o[(p0 + u) * dim + q0 + w] = keep ? acc[u][w] : T(0);
+            img[(p0 + u) * dim + q0 + w] = keep ? acc[u][w] : T(0);
           }
     }
+    // the sample's matrix is contiguous in memory: it leaves as one linear copy (the tiles' own 4 x 4 patches would be
+    // sixteen strided scalar stores per thread)
+    __syncthreads();
+    for (int i = threadIdx.x; i < dim * dim; i += blockDim.x) o[i] = img[i];
   }
 }
 
@@ -347,19 +365,30 @@ template <typename T>
 int wig_launch(bool backward, const eqt_wigner_table* t, WigArgs a, cudaStream_t st) {
   const int L1 = t->max_l + 1;
   if (!backward) {
-    const size_t bytes = sizeof(T) * ((size_t)t->coef_count + WIG_EPB * 3 * L1 * 2) + sizeof(int32_t) * t->dim * t->dim;
+    a.block_elems = t->dim * t->dim;
+    const size_t bytes = sizeof(T) * ((size_t)t->coef_count + WIG_EPB * 3 * L1 * 2 + (size_t)t->dim * t->dim) +
+                         sizeof(int32_t) * 2 * a.block_elems;
     if (t->max_l > 7 || t->coef_count >= (1 << 19)) return fail(EQT_ERR_UNSUPPORTED, "element codes hold degrees up to 7");
     if (bytes > 200 * 1024) return fail(EQT_ERR_UNSUPPORTED, "Wigner coefficient table too large for shared memory");
     cudaError_t e = cudaFuncSetAttribute(wigner_d_forward_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
     if (e != cudaSuccess) return fail(EQT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    wigner_d_forward_kernel<T><<<flat_grid(ceil_div(a.n, WIG_EPB), 1, 8), 256, bytes, st>>>(a);
+    // one resident wave (the per-CTA tables make a second, partial wave expensive)
+    int per_sm = 1;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, wigner_d_forward_kernel<T>, 256, bytes) != cudaSuccess || per_sm < 1)
+      per_sm = 1;
+    const unsigned grid = (unsigned)std::min<int64_t>(ceil_div(a.n, WIG_EPB), (int64_t)sm_count() * per_sm);
+    wigner_d_forward_kernel<T><<<grid, 256, bytes, st>>>(a);
     return check_launch("wigner_d_forward_kernel");
   }
   const size_t bytes = sizeof(T) * ((size_t)t->coef_count + 8 * 3 * L1 * 2);
   if (bytes > 200 * 1024) return fail(EQT_ERR_UNSUPPORTED, "Wigner coefficient table too large for shared memory");
   cudaError_t e = cudaFuncSetAttribute(wigner_d_backward_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
   if (e != cudaSuccess) return fail(EQT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-  wigner_d_backward_kernel<T><<<flat_grid(ceil_div(a.n, 8), 1, 8), 256, bytes, st>>>(a, t->num_blocks, t->blocks);
+  int per_sm = 1;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, wigner_d_backward_kernel<T>, 256, bytes) != cudaSuccess || per_sm < 1)
+    per_sm = 1;
+  const unsigned grid = (unsigned)std::min<int64_t>(ceil_div(a.n, 8), (int64_t)sm_count() * per_sm);
+  wigner_d_backward_kernel<T><<<grid, 256, bytes, st>>>(a, t->num_blocks, t->blocks);
   return check_launch("wigner_d_backward_kernel");
 }
 
@@ -434,7 +463,7 @@ extern "C" int eqt_dense_rotation_grad_matrix(const void* grad_out, const void* 
   if (n == 0) return EQT_OK;
   if (!grad_out || !x || !grad_matrix) return fail(EQT_ERR_BAD_ARGUMENT, "NULL pointer");
   const size_t es = dtype == EQT_F32 ? 4 : 8;
-  const size_t bytes = es * 2 * (size_t)channels * ((dim + 3) & ~3);
+  const size_t bytes = es * (2 * (size_t)channels * ((dim + 3) & ~3) + (size_t)dim * dim);
   if (bytes > 200 * 1024) return fail(EQT_ERR_UNSUPPORTED, "features of one sample do not fit shared memory");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   auto wave = [&](auto kernel, int threads) {

@@ -149,4 +149,4 @@ def rotation_supported(matrix: Tensor, x: Tensor) -> bool:
         return False
     es = x.element_size()
     d4, c4 = (d + 3) // 4 * 4, (c + 3) // 4 * 4
-    return es * (d * d4 + d * c4) <= 200 * 1024 and es * 2 * c * d4 <= 200 * 1024
+    return es * (d * d4 + d * c4) <= 200 * 1024 and es * (2 * c * d4 + d * d) <= 200 * 1024
