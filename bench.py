@@ -674,7 +674,7 @@ def main():
             read_back[i % 2].record(main_stream)
             if i > 0:
                 read_back[(i - 1) % 2].synchronize()
-                results.append(float(loss_host[(i - 1) % 2]))
+                results.append(float(loss_host[(i - 1) % 2].detach()))
         read_back[(count - 1) % 2].synchronize()
         results.append(float(loss_host[(count - 1) % 2]))
 

@@ -112,18 +112,20 @@ __global__ void __launch_bounds__(256) ew_kernel(P p) {
 }
 
 // float, C % 4 == 0, 16-byte aligned operands: four channels per thread, 128-bit accesses.
-template <int OP>
+// I: index type of the flattened (sample, output row, channel group) loop; 32-bit when the count fits (64-bit
+// divisions cost more than the loads of an element).
+template <int OP, typename I>
 __global__ void __launch_bounds__(256) ew_kernel_f4(P p) {
   const float* x = static_cast<const float*>(p.in1);
   const float* y = static_cast<const float*>(p.in2);
   float* out = static_cast<float*>(p.out);
-  const int64_t C = p.c1, C4 = C / 4;
-  const int64_t total = p.n * p.num_out * C4;
-  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
-       idx += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t c = (idx % C4) * 4;
-    const int64_t o = (idx / C4) % p.num_out;
-    const int64_t n = idx / (C4 * p.num_out);
+  const int64_t C = p.c1;
+  const I C4 = (I)(C / 4), num_out = (I)p.num_out;
+  const I total = (I)(p.n * p.num_out * (C / 4));
+  for (I idx = (I)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (I)gridDim.x * blockDim.x) {
+    const int64_t c = (int64_t)(idx % C4) * 4;
+    const int64_t o = (int64_t)((idx / C4) % num_out);
+    const int64_t n = (int64_t)(idx / (C4 * num_out));
     int64_t t0, t1;
     seg_range(p, o, t0, t1);
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -212,7 +214,43 @@ __global__ void __launch_bounds__(256) ew_acc_kernel(P p, int64_t chunk) {
   int64_t t0, t1;
   seg_range(p, o, t0, t1);
   A acc = 0;
-  if (c < C) {
+  // The entries of the output row are the same for every sample: they are staged in shared memory once (up to
+  // ACC_STAGE of them), and four samples are in flight per thread - with one, a thread waited for the latency of
+  // memory at every sample and the kernel ran at a seventh of the bandwidth.
+  constexpr int ACC_STAGE = 64;
+  __shared__ int32_t e_r1[ACC_STAGE], e_r2[ACC_STAGE];
+  __shared__ A e_sc[ACC_STAGE];
+  const bool staged = t1 - t0 <= ACC_STAGE;
+  if (staged) {
+    const int tid = threadIdx.y * 32 + threadIdx.x;
+    if (tid < t1 - t0) {
+      const Entry e = entry(p, t0 + tid);
+      e_r1[tid] = (int32_t)e.r1;
+      e_r2[tid] = (int32_t)e.r2;
+      e_sc[tid] = scale_of<T>(p, e.tt);
+    }
+    __syncthreads();
+  }
+  if (c < C && staged) {
+    const int ne = (int)(t1 - t0);
+    for (int64_t n = n0 + threadIdx.y; n < n1; n += 32) {
+      A part[4] = {0, 0, 0, 0};
+      for (int t = 0; t < ne; ++t) {
+        const int64_t o1 = (int64_t)e_r1[t] * C + c, o2 = OP == EQT_OP_MUL ? (int64_t)e_r2[t] * C + c : (int64_t)e_r2[t];
+        const A sc = e_sc[t];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int64_t nn = n + 8 * u;
+          if (nn < n1) {
+            A v = ld(x + nn * p.bs1 + o1);
+            if (OP == EQT_OP_MUL || OP == EQT_OP_VECSCA) v *= ld(y + nn * p.bs2 + o2);
+            part[u] += v * sc;
+          }
+        }
+      }
+      acc += (part[0] + part[1]) + (part[2] + part[3]);
+    }
+  } else if (c < C) {
     for (int64_t n = n0 + threadIdx.y; n < n1; n += 8) {
       for (int64_t t = t0; t < t1; ++t) {
         const Entry e = entry(p, t);
@@ -489,10 +527,17 @@ int launch(const eqt_product_args& a, P p, cudaStream_t s) {
     }
     if (std::is_same<T, float>::value && p.c1 % 4 == 0 && aligned16(p.in1) && aligned16(p.out) &&
         (op != EQT_OP_MUL || aligned16(p.in2))) {
-      const unsigned grid = flat_grid(p.n * p.num_out * (p.c1 / 4), 256);
-      if (op == EQT_OP_MUL) ew_kernel_f4<EQT_OP_MUL><<<grid, 256, 0, s>>>(p);
-      if (op == EQT_OP_VECSCA) ew_kernel_f4<EQT_OP_VECSCA><<<grid, 256, 0, s>>>(p);
-      if (op == EQT_OP_SCALE) ew_kernel_f4<EQT_OP_SCALE><<<grid, 256, 0, s>>>(p);
+      const int64_t work = p.n * p.num_out * (p.c1 / 4);
+      const unsigned grid = flat_grid(work, 256);
+      if (work + (int64_t)grid * 256 < (int64_t(1) << 32)) {      // the strided index cannot wrap
+        if (op == EQT_OP_MUL) ew_kernel_f4<EQT_OP_MUL, uint32_t><<<grid, 256, 0, s>>>(p);
+        if (op == EQT_OP_VECSCA) ew_kernel_f4<EQT_OP_VECSCA, uint32_t><<<grid, 256, 0, s>>>(p);
+        if (op == EQT_OP_SCALE) ew_kernel_f4<EQT_OP_SCALE, uint32_t><<<grid, 256, 0, s>>>(p);
+      } else {
+        if (op == EQT_OP_MUL) ew_kernel_f4<EQT_OP_MUL, int64_t><<<grid, 256, 0, s>>>(p);
+        if (op == EQT_OP_VECSCA) ew_kernel_f4<EQT_OP_VECSCA, int64_t><<<grid, 256, 0, s>>>(p);
+        if (op == EQT_OP_SCALE) ew_kernel_f4<EQT_OP_SCALE, int64_t><<<grid, 256, 0, s>>>(p);
+      }
       return check_launch("ew_kernel_f4");
     }
     if (std::is_same<T, __nv_bfloat16>::value && p.c1 % 8 == 0 && aligned16(p.in1) && aligned16(p.out) &&
