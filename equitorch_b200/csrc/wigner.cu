@@ -307,12 +307,49 @@ __global__ void __launch_bounds__(256) dense_rotation_grad_matrix_kernel(const T
     __syncthreads();
     // consecutive threads read consecutive channels of one row (coalesced); the transposing store is padded by the
     // row pitch dim4 (odd multiples of four words spread over the banks well enough for this one pass)
-    for (int r = threadIdx.x / 32; r < dim; r += blockDim.x / 32)
-      for (int k = threadIdx.x % 32; k < c; k += 32) {
-        cp_async<sizeof(T)>(gs + k * dim4 + r, g + (s * dim + r) * c + k);
-        cp_async<sizeof(T)>(xs + k * dim4 + r, x + (s * dim + r) * c + k);
+    const T* gsrc = g + s * dim * c;
+    const T* xsrc = x + s * dim * c;
+    bool staged = false;
+    if constexpr (sizeof(T) == 4) {
+     if ((c & 3) == 0 && ((reinterpret_cast<uintptr_t>(gsrc) | reinterpret_cast<uintptr_t>(xsrc)) & 15u) == 0) {
+      staged = true;
+      // 16-byte loads of both operands first (all in flight), then the transposing scalar stores: element-wise
+      // asynchronous copies to transposed addresses ran at about one element per cycle and SM
+      const int quads = dim * c / 4;
+      for (int i0 = threadIdx.x; i0 < quads; i0 += 2 * blockDim.x) {
+        float4 gv[2], xv[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int i = i0 + u * blockDim.x;
+          if (i < quads) {
+            gv[u] = __ldg(reinterpret_cast<const float4*>(gsrc) + i);
+            xv[u] = __ldg(reinterpret_cast<const float4*>(xsrc) + i);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int i = i0 + u * blockDim.x;
+          if (i < quads) {
+            const int r = (i * 4) / c, k = (i * 4) % c;
+            const float ga[4] = {gv[u].x, gv[u].y, gv[u].z, gv[u].w}, xa[4] = {xv[u].x, xv[u].y, xv[u].z, xv[u].w};
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+              gs[(k + w) * dim4 + r] = ga[w];
+              xs[(k + w) * dim4 + r] = xa[w];
+            }
+          }
+        }
       }
-    cp_async_wait_all();
+     }
+    }
+    if (!staged) {
+      for (int r = threadIdx.x / 32; r < dim; r += blockDim.x / 32)
+        for (int k = threadIdx.x % 32; k < c; k += 32) {
+          cp_async<sizeof(T)>(gs + k * dim4 + r, gsrc + r * c + k);
+          cp_async<sizeof(T)>(xs + k * dim4 + r, xsrc + r * c + k);
+        }
+      cp_async_wait_all();
+    }
     __syncthreads();
     T* o = gm + s * dim * dim;
     for (int i = threadIdx.x; i < groups * groups; i += blockDim.x) {

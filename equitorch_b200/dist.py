@@ -176,8 +176,8 @@ class _ShardedLayer(torch.autograd.Function):
         if _distributed(group):
             dist.all_to_all_single(buf[n_owned:], buf[:n_owned].index_select(0, send_index), plan.recv_counts,
                                    plan.send_counts, group=group)
-        elif buf.shape[0] > n_owned:       # single process holding a plan with halo rows: they are its own rows
-            buf[n_owned:] = buf[:n_owned].index_select(0, send_index)[: buf.shape[0] - n_owned]
+        elif buf.shape[0] > n_owned:
+            raise RuntimeError("the plan has halo rows, but no process group with more than one rank is initialised")
         out, state = ops.forward(buf, y, weight)
         ctx.ops, ctx.plan, ctx.group, ctx.state = ops, plan, group, state
         ctx.save_for_backward(send_index)
@@ -208,8 +208,6 @@ class _ShardedLayer(torch.autograd.Function):
             if work_x is not None:
                 work_x.wait()
                 gx[:n_owned].index_add_(0, send_index, back)
-            elif gx.shape[0] > n_owned:
-                gx[:n_owned].index_add_(0, send_index[: gx.shape[0] - n_owned], gx[n_owned:])
             gx[n_owned:].zero_()
         if work_w is not None:
             work_w.wait()
