@@ -218,16 +218,18 @@ extern "C" int eqt_mix_tc_transposed(const float* g, const float* w_big, const f
 namespace eqt {
 namespace {
 
-// Launch of the weight-gradient kernel instance for `n_cols` output columns.
-int launch_wgrad(dim3 grid, size_t smem, cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mb, const WgradArgs& a) {
-  cudaError_t e = a.n_cols <= 64
+// Launch of the weight-gradient kernel instance for the batch's output columns: one CTA per (block, split, M slice).
+int launch_wgrad(const WgradBatch& b, size_t smem, cudaStream_t st) {
+  cudaError_t e = b.n_cols <= 64
                       ? cudaFuncSetAttribute(wgrad_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)
                       : cudaFuncSetAttribute(wgrad_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
   if (e != cudaSuccess) return fail(EQT_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-  if (a.n_cols <= 64)
-    wgrad_tc_kernel<64><<<grid, WgradCfg<64>::THREADS, smem, st>>>(ma, mb, a);
+  const WgradBlock& last = b.blk[b.count - 1];
+  const unsigned grid = (unsigned)(last.cta_begin + last.splits * last.m_tiles);
+  if (b.n_cols <= 64)
+    wgrad_tc_kernel<64><<<grid, WgradCfg<64>::THREADS, smem, st>>>(b);
   else
-    wgrad_tc_kernel<128><<<grid, WgradCfg<128>::THREADS, smem, st>>>(ma, mb, a);
+    wgrad_tc_kernel<128><<<grid, WgradCfg<128>::THREADS, smem, st>>>(b);
   return check_launch("wgrad_tc_kernel");
 }
 
@@ -264,11 +266,13 @@ extern "C" int64_t eqt_wgrad_tc_scratch_floats(int64_t n, int32_t cin, int32_t c
                                                int32_t num_blocks) {
   using namespace eqt;
   if (n < 0 || cin <= 0 || cout <= 0 || cin % 32 || cout % 32 || num_blocks < 0 || (num_blocks && !blocks)) return -1;
+  // the sum over the blocks: with that much scratch all blocks run in one launch; eqt_wgrad_tc also works with the
+  // largest block's need alone (one launch per block then)
   int64_t need = 0;
   for (int b = 0; b < num_blocks; ++b) {
     WgradShape w{};
     if (wgrad_shape(blocks[b], b, std::max<int64_t>(n, 1), cin, cout, &w)) return -1;
-    need = std::max(need, w.need);
+    need += w.need;
   }
   return need;
 }
@@ -290,40 +294,55 @@ extern "C" int eqt_wgrad_tc(const float* s, const float* g, float* gw_packed, fl
       return fail(EQT_ERR_BAD_ARGUMENT, "scratch too small: block %d needs %lld floats, %lld given", b,
                   (long long)shapes[b].need, (long long)scratch_floats);
   }
-  for (int b = 0; b < num_blocks; ++b) {
-    const eqt_mix_block& blk = blocks[b];
-    const WgradShape& w = shapes[b];
-    const int64_t K = w.K;
-    const int m_tiles = w.m_tiles, npt = w.npt, splits = w.splits;
-    const size_t stage_bytes = w.stage_bytes;
-    WgradArgs a{};
-    a.n = n; a.dim = blk.dim; a.npt = npt; a.rows_pad = w.rows_pad; a.n_cols = cout; a.status = status;
-    a.stages = w.stages;
-    a.issuers = w.rows_pad / 8 >= 2 ? 2 : 1;
-    a.tmem_cols = 32;
-    while (a.tmem_cols < 2 * a.issuers * cout) a.tmem_cols <<= 1;
-    a.chunk_tiles = w.chunk_tiles;
-    a.partial = scratch;
-    CUtensorMap map_s, map_g;
-    {
-      cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)blk.dim, (cuuint64_t)n};
-      cuuint64_t strides[2] = {(cuuint64_t)K * 4, (cuuint64_t)rows * cin * 4};
-      cuuint32_t box[3] = {KB, (cuuint32_t)blk.dim, (cuuint32_t)npt};
-      if (int rc = make_map(&map_s, s + (int64_t)blk.in_row0 * cin, 3, dims, strides, box,
-                            CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return rc;
+  int64_t total_need = 0;
+  for (int b = 0; b < num_blocks; ++b) total_need += shapes[b].need;
+  // With scratch for every block at once, up to WGRAD_MAX_BLOCKS blocks share a launch (and one reduction launch);
+  // otherwise the blocks run one after the other and reuse the scratch.
+  const int per_launch = total_need <= scratch_floats ? WGRAD_MAX_BLOCKS : 1;
+  for (int b0 = 0; b0 < num_blocks; b0 += per_launch) {
+    const int count = std::min(per_launch, num_blocks - b0);
+    WgradBatch B{};
+    ReduceBatch R{};
+    B.count = R.count = count;
+    B.n = n; B.n_cols = R.cols = cout; B.status = status;
+    B.tmem_cols = 32;
+    size_t smem = 0;
+    int cta = 0;
+    int64_t scratch_at = 0, quads = 0;
+    for (int q = 0; q < count; ++q) {
+      const eqt_mix_block& blk = blocks[b0 + q];
+      const WgradShape& w = shapes[b0 + q];
+      WgradBlock& a = B.blk[q];
+      a.dim = blk.dim; a.npt = w.npt; a.rows_pad = w.rows_pad; a.stages = w.stages; a.chunk_tiles = w.chunk_tiles;
+      a.issuers = w.rows_pad / 8 >= 2 ? 2 : 1;
+      a.m_tiles = w.m_tiles; a.splits = w.splits; a.cta_begin = cta;
+      a.partial = scratch + scratch_at;
+      cta += w.splits * w.m_tiles;
+      while (B.tmem_cols < 2 * a.issuers * cout) B.tmem_cols <<= 1;
+      smem = std::max(smem, (size_t)w.stages * w.stage_bytes + 1024);
+      {
+        cuuint64_t dims[3] = {(cuuint64_t)w.K, (cuuint64_t)blk.dim, (cuuint64_t)n};
+        cuuint64_t strides[2] = {(cuuint64_t)w.K * 4, (cuuint64_t)rows * cin * 4};
+        cuuint32_t box[3] = {KB, (cuuint32_t)blk.dim, (cuuint32_t)w.npt};
+        if (int rc = make_map(&a.map_s, s + (int64_t)blk.in_row0 * cin, 3, dims, strides, box,
+                              CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return rc;
+      }
+      {
+        cuuint64_t dims[3] = {(cuuint64_t)cout, (cuuint64_t)blk.dim, (cuuint64_t)n};
+        cuuint64_t strides[2] = {(cuuint64_t)cout * 4, (cuuint64_t)comps * cout * 4};
+        cuuint32_t box[3] = {KB, (cuuint32_t)blk.dim, (cuuint32_t)w.npt};
+        if (int rc = make_map(&a.map_g, g + (int64_t)blk.out_row0 * cout, 3, dims, strides, box,
+                              CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return rc;
+      }
+      R.blk[q].partial = a.partial; R.blk[q].out = gw_packed + blk.w_offset; R.blk[q].splits = w.splits;
+      R.blk[q].padded_rows = (int64_t)w.m_tiles * 128; R.blk[q].begin = quads;
+      quads += w.K * cout / 4;
+      scratch_at += w.need;
     }
-    {
-      cuuint64_t dims[3] = {(cuuint64_t)cout, (cuuint64_t)blk.dim, (cuuint64_t)n};
-      cuuint64_t strides[2] = {(cuuint64_t)cout * 4, (cuuint64_t)comps * cout * 4};
-      cuuint32_t box[3] = {KB, (cuuint32_t)blk.dim, (cuuint32_t)npt};
-      if (int rc = make_map(&map_g, g + (int64_t)blk.out_row0 * cout, 3, dims, strides, box,
-                            CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return rc;
-    }
-    dim3 grid((unsigned)splits, (unsigned)m_tiles);
-    if (int rc = launch_wgrad(grid, (size_t)a.stages * stage_bytes + 1024, st, map_s, map_g, a)) return rc;
-    wgrad_reduce_kernel<<<flat_grid(K * cout / 4, 256), 256, 0, st>>>(scratch, gw_packed + blk.w_offset, splits,
-                                                                      (int64_t)m_tiles * 128, K, cout);
-    if (int rc = check_launch("wgrad_reduce_kernel")) return rc;
+    R.total = quads;
+    if (int rc = launch_wgrad(B, smem, st)) return rc;
+    wgrad_reduce_batched_kernel<<<flat_grid(quads, 256), 256, 0, st>>>(R);
+    if (int rc = check_launch("wgrad_reduce_batched_kernel")) return rc;
   }
   return EQT_OK;
 }
@@ -411,13 +430,15 @@ extern "C" int eqt_outer_tc(const float* in1, const float* in2, float* out, floa
     const size_t budget = 220 * 1024 - 1024;
     const size_t bytes_per_row = 2 * (size_t)(4 + b_boxes) * 128;
     const int npt = std::max(8, (int)(budget / 3 / bytes_per_row) / 8 * 8);          // reduction rows per tile
-    WgradArgs a{};
-    a.n = n; a.dim = 1; a.npt = npt; a.rows_pad = npt; a.n_cols = c2; a.status = status;
+    WgradBatch B{};
+    B.count = 1; B.n = n; B.n_cols = c2; B.status = status;
+    WgradBlock& a = B.blk[0];
+    a.dim = 1; a.npt = npt; a.rows_pad = npt;
     const size_t stage_bytes = bytes_per_row * (size_t)npt;
     a.stages = (int)std::min<size_t>(8, budget / stage_bytes);
     a.issuers = npt / 8 >= 2 ? 2 : 1;
-    a.tmem_cols = 32;
-    while (a.tmem_cols < 2 * a.issuers * c2) a.tmem_cols <<= 1;
+    B.tmem_cols = 32;
+    while (B.tmem_cols < 2 * a.issuers * c2) B.tmem_cols <<= 1;
     a.chunk_tiles = std::max(1, 512 / npt);
     a.a_cols = a_cols; a.b_cols = b_cols;
     const int64_t tiles = ceil_div(n, npt);
@@ -425,21 +446,20 @@ extern "C" int eqt_outer_tc(const float* in1, const float* in2, float* out, floa
     const int64_t need = (int64_t)splits * m_tiles * 128 * c2;
     if (need > scratch_floats) return fail(EQT_ERR_BAD_ARGUMENT, "scratch too small: %lld floats needed", (long long)need);
     a.partial = scratch;
-    CUtensorMap map_a, map_b;
+    a.m_tiles = m_tiles; a.splits = splits; a.cta_begin = 0;
     {
       cuuint64_t dims[3] = {(cuuint64_t)rows1 * c1, 1, (cuuint64_t)n};
       cuuint64_t strides[2] = {(cuuint64_t)rows1 * c1 * 4, (cuuint64_t)rows1 * c1 * 4};
       cuuint32_t box[3] = {KB, 1, (cuuint32_t)npt};
-      if (int rc = make_map(&map_a, in1, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return rc;
+      if (int rc = make_map(&a.map_s, in1, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return rc;
     }
     {
       cuuint64_t dims[3] = {(cuuint64_t)rows2 * c2, 1, (cuuint64_t)n};
       cuuint64_t strides[2] = {(cuuint64_t)rows2 * c2 * 4, (cuuint64_t)rows2 * c2 * 4};
       cuuint32_t box[3] = {KB, 1, (cuuint32_t)npt};
-      if (int rc = make_map(&map_b, in2, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return rc;
+      if (int rc = make_map(&a.map_g, in2, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return rc;
     }
-    dim3 grid((unsigned)splits, (unsigned)m_tiles);
-    if (int rc = launch_wgrad(grid, (size_t)a.stages * stage_bytes + 1024, st, map_a, map_b, a)) return rc;
+    if (int rc = launch_wgrad(B, (size_t)a.stages * stage_bytes + 1024, st)) return rc;
   }
   // with no samples or no entries every unit list is read as empty only if m_tiles == 0; otherwise the partial sums
   // above were written by this call
