@@ -222,10 +222,12 @@ int eqt_mix_tc_transposed(const float* g, const float* w_big, const float* w_sma
  *   gw_packed[w_offset + (p*cin + ci)*cout + co] = sum_i sum_m s[i, in_row0 + m*paths + p, ci] * g[i, out_row0 + m, co]
  * i.e. per block a (paths*cin, cout) row-major matrix, the same stacking as the weights handed to
  * eqt_mix_tc_transposed.  The sum over the n samples is split over CTAs; their float32 partial sums go
- * through `scratch` (at least eqt_wgrad_tc_scratch_floats(...) floats - 128 * cout * #SMs unless a block has
- * more than 128 * #SMs stacked input channels; caller-owned, contents undefined afterwards) and are reduced
- * in a fixed order: no atomics, results are bit-reproducible.  All blocks are checked before the first
- * launch: an error return leaves gw_packed untouched.
+ * through `scratch` (caller-owned, contents undefined afterwards) and are reduced in a fixed order: no atomics,
+ * results are bit-reproducible.  A block needs 128 * cout * #SMs floats of scratch (more only with over
+ * 128 * #SMs stacked input channels).  With eqt_wgrad_tc_scratch_floats(...) floats - the sum over the blocks -
+ * all blocks run in one launch; with at least the largest block's need they run one launch per block and share
+ * the scratch; the results are the same bit for bit.  All blocks are checked before the first launch: an error
+ * return leaves gw_packed untouched.
  * Needs cin % 32 == 0, cout % 32 == 0, cout <= 128.
  * replaces: indexed_outer_scale_gather with out_accumulated=True on the `info_M_bwd2` table
  *   (equitorch/nn/functional/linears.py:316-320), which uses atomic adds in the reference.
@@ -233,8 +235,8 @@ int eqt_mix_tc_transposed(const float* g, const float* w_big, const float* w_sma
 int eqt_wgrad_tc(const float* s, const float* g, float* gw_packed, float* scratch, int64_t scratch_floats, int64_t n,
                  int32_t rows, int32_t comps, int32_t cin, int32_t cout, const eqt_mix_block* blocks,
                  int32_t num_blocks, int32_t* status, void* stream);
-/* Floats of scratch eqt_wgrad_tc needs for these blocks on the current device, or -1 for blocks it refuses
- * (host-side arithmetic only; part of the eqt_wgrad_tc interface above). */
+/* Floats of scratch with which eqt_wgrad_tc runs these blocks in one launch on the current device (the sum of the
+ * blocks' needs), or -1 for blocks it refuses (host-side arithmetic only; part of the eqt_wgrad_tc interface above). */
 int64_t eqt_wgrad_tc_scratch_floats(int64_t n, int32_t cin, int32_t cout, const eqt_mix_block* blocks, int32_t num_blocks);
 
 /*
@@ -285,8 +287,8 @@ int64_t eqt_outer_tc_scratch_floats(int64_t n, int32_t c2, int32_t m_tiles);
  * eqt_wgrad_tc minus `scratch`; the per-CTA partial sums go through a 4.85 MB array that is part of the
  * library image on every GPU (148 x 128 x 64 floats, eqt_wgrad_tc_static_capacity()).  The function
  * and everything it calls allocate nothing.
- *   - Limit: cout <= 64 and eqt_wgrad_tc_scratch_floats(...) (#SMs * 128 * cout for ordinary layers) must
- *     fit the array; larger requests return EQT_ERR_UNSUPPORTED with a message naming the limit, before
+ *   - Limit: cout <= 64 and every block's own need (#SMs * 128 * cout for ordinary layers) must fit the array
+ *     (the blocks run one launch each and share it); larger requests return EQT_ERR_UNSUPPORTED with a message naming the limit, before
  *     anything is launched - use eqt_wgrad_tc then.
  *   - The first call on each device looks up the array's device address (with that device current);
  *     make that first call outside any stream capture.
