@@ -72,6 +72,31 @@ def test_fused_graph_layer_equals_per_edge_layer_plus_scatter():
     assert err < 1e-5, f"relative error {err:.2e}"
 
 
+def test_forward_sharded_on_one_rank_equals_forward():
+    """`forward_sharded` with a one-rank plan (no halo rows, no process group): same output and the same three
+    gradients as `forward`, although its backward pass runs the passes in another order (local-row gradient first)."""
+    from equitorch_b200.dist import plan_shards
+    nodes, edges, c, ir = 60, 900, 64, "0e+1o+2e+3o"
+    g, src, dst, vec = _case(12, nodes, edges)
+    order = torch.argsort(dst, stable=True)
+    src, dst, vec = src[order], dst[order], vec[order]
+    plan = plan_shards(src, dst, nodes, 1)[0]
+    assert plan.num_local == nodes and plan.send_index.numel() == 0
+    layer = enn.SO3LinearGraph(ir, ir, ir, c, c, feature_mode="uv").to(DEV)
+    graph = EdgeGraph(plan.src_local.to(DEV), plan.dst_local.to(DEV), plan.num_local, plan.num_owned)
+    cot = torch.randn(nodes, 16, c, generator=g).to(DEV)
+    results = []
+    for sharded in (False, True):
+        x = torch.randn(nodes, 16, c, generator=torch.Generator().manual_seed(5)).to(DEV).requires_grad_(True)
+        v = vec.to(DEV).requires_grad_(True)
+        y = enn.SphericalHarmonics(3)(v)
+        out = layer.forward_sharded(x, y, graph, plan) if sharded else layer(x, y, graph)
+        results.append((out, *torch.autograd.grad(out, [x, v, layer.weight], cot)))
+    check_status()
+    for a, b in zip(*results):
+        torch.testing.assert_close(a, b, rtol=0, atol=0)
+
+
 def test_fused_graph_layer_no_edges_and_rectangular():
     ir, c = "0e+1o+2e", 64
     layer = enn.SO3LinearGraph(ir, ir, ir, c, c, feature_mode="uv").to(DEV)
