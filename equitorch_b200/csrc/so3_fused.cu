@@ -857,8 +857,7 @@ int launch_spec(bool inner, const FusedArgs& a, cudaStream_t s) {
 
 // the tensor-core kernel pays when nodes have several edges each (groups of eight) and everything is 16-byte aligned
 inline bool segsum_tc_wanted(const FusedArgs& a) {
-  static const bool enabled = [] { const char* v = getenv("EQT_SEGSUM_TC"); return !(v && v[0] == '0'); }();
-  return enabled && a.ptr && a.C == 64 && a.n_edges >= 4 * a.n_out && a.n_out < 0x7fffffffll && (reinterpret_cast<uintptr_t>(a.y) & 15u) == 0 &&
+  return a.ptr && a.C == 64 && a.n_edges >= 4 * a.n_out && a.n_out < 0x7fffffffll && (reinterpret_cast<uintptr_t>(a.y) & 15u) == 0 &&
          (reinterpret_cast<uintptr_t>(a.out) & 15u) == 0;
 }
 
